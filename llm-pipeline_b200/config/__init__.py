@@ -6,7 +6,8 @@ from .registry import (architecture_name, load_config, register_architecture, re
 from .qwen3 import Qwen3Config
 from .zupilorn import ZupilornConfig
 from .razelorn import RazelornConfig
+from .nufolix import NufolixConfig
 
-__all__ = ["LayerSpec", "ModelConfig", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen3Config", "ZupilornConfig", "RazelornConfig",
+__all__ = ["LayerSpec", "ModelConfig", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen3Config", "ZupilornConfig", "RazelornConfig", "NufolixConfig",
            "architecture_name", "load_config", "register_architecture", "resolve_config",
            "supported_architectures"]

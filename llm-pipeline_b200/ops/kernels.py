@@ -77,6 +77,15 @@ _SIGNATURES = {
     "llmp_diff_attention": [_P, _L, _P, _I, _P, _I, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _P],
     "llmp_diff_attention_mma": [_P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F,
                                 _I, _I, _I, _P, _P, _P],
+    "llmp_short_conv": [_P, _L, _P, _I, _P, _I, _P, _L, _L, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P],
+    "llmp_ssd_scan": [_P, _L, _P, _L, _P, _P, _P, _P, _L, _L, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _P],
+    "llmp_gated_group_norm": [_P, _L, _P, _L, _P, _P, _I, _L, _I, _I, _I, _I, _F, _P],
+    "llmp_delta_prep": [_P, _L, _P, _L, _P, _L, _P, _L, _P, _P, _I, _I, _I, _I, _P],
+    "llmp_delta_scan": [_P, _L, _P, _L, _P, _L, _P, _L, _P, _L, _P, _L, _L, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _P],
+    "llmp_sig_qkv_post": [_P, _L, _P, _I, _P, _P, _I, _P, _I, _L, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "llmp_sigmoid_attention": [_P, _L, _P, _I, _P, _I, _P, _P, _P, _P, _P, _L, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P],
+    "llmp_xielu": [_P, _P, _I, _F, _F, _P, _I, _L, _I, _P],
+    "llmp_scaled_sum": [_P, _F, _P, _F, _P, _L, _P],
 }
 _bound = {}
 launch_count = 0   # kernels of this library launched so far (captured launches count once per capture)
@@ -1159,4 +1168,181 @@ def diff_attention_mma(q: torch.Tensor, pages: torch.Tensor, tables: torch.Tenso
           dim, vdim, pages.shape[2], int(window), float(scale), float(lam), float(eps), float(out_scale),
           DIFF_SEGMENT_KEYS if segments > 0 else 0, int(segments), 1 if split and segments > 0 else 0, _ptr(scratch), _ptr(counters),
           _stream())
+    return out
+
+
+SHORT_CONV_MAX_TAPS = 8           # taps the short-convolution kernels hold in registers
+
+
+def _state_views(state: torch.Tensor, offset: int, half: int, name: str):
+    """A request's state slot is one float32 vector ``state[slot, :]``; a part keeps a piece of it that starts at ``offset``
+    and holds two copies of ``half`` entries, which take turns by the parity of the last position written."""
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1, f"{name}: the state must be float32 [slots, entries]")
+    _need(0 <= offset and offset + 2 * half <= state.shape[1], f"{name}: the state piece does not fit the slot")
+    return state.data_ptr() + 4 * offset, state.stride(0), half
+
+
+def short_conv(x: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor, state_offset: int,
+               q_start: torch.Tensor, slots: torch.Tensor, positions: torch.Tensor, token_request: torch.Tensor, out: torch.Tensor,
+               max_q_len: int, silu: bool = True) -> torch.Tensor:
+    """Causal convolution over time per channel with its carried inputs: ``x`` float32 [tokens, C] (a view with a dense last
+    axis), ``taps`` [C, K] (the last column multiplies the current token), ``bias`` [C] or None, ``out`` float32 [tokens, C].
+    The state piece holds two copies of the request's last K - 1 inputs [K - 1, C]."""
+    N, C = x.shape
+    K = taps.shape[1]
+    _need(x.dtype == torch.float32 and x.stride(1) == 1 and out.dtype == torch.float32 and out.stride(1) == 1 and out.shape == (N, C),
+          "short_conv takes float32 rows")
+    _need(taps.shape[0] == C and taps.is_contiguous() and (bias is None or (bias.numel() == C and bias.is_contiguous())),
+          "short_conv: taps or bias have the wrong shape")
+    for t, name in ((q_start, "q_start"), (slots, "slots"), (positions, "positions"), (token_request, "token_request")):
+        _i32(t, name)
+    ptr, slot_stride, half = _state_views(state, state_offset, (K - 1) * C, "short_conv")
+    _call("llmp_short_conv", _ptr(x), x.stride(0), _ptr(taps), dtype_code(taps.dtype), _ptr(bias),
+          dtype_code(bias.dtype) if bias is not None else F32, ptr, slot_stride, half, _ptr(q_start), _ptr(slots), _ptr(positions),
+          _ptr(token_request), _ptr(out), out.stride(0), N, slots.numel(), C, K, 1 if silu else 0, int(max_q_len), _stream())
+    return out
+
+
+def ssd_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
+             state: torch.Tensor, state_offset: int, q_start: torch.Tensor, slots: torch.Tensor, positions: torch.Tensor,
+             y: torch.Tensor, heads: int, groups: int, state_size: int, vdim: int) -> torch.Tensor:
+    """The state-space recurrence with a scalar decay per head and token (csrc/state_space.cu): ``xbc`` float32 [tokens,
+    heads vdim + 2 groups state] = x | B | C, ``dt`` float32 [tokens, heads] (a view), the three per-head vectors float32,
+    ``y`` float32 [tokens, heads vdim]. The state piece holds two copies of [heads, state, vdim]."""
+    N = xbc.shape[0]
+    _need(xbc.dtype == torch.float32 and xbc.stride(1) == 1 and xbc.shape[1] == heads * vdim + 2 * groups * state_size,
+          "ssd_scan: x | B | C has the wrong width")
+    _need(dt.dtype == torch.float32 and dt.stride(1) == 1 and dt.shape == (N, heads), "ssd_scan: dt must be float32 [tokens, heads]")
+    _need(y.dtype == torch.float32 and y.stride(1) == 1 and y.shape == (N, heads * vdim), "ssd_scan: y has the wrong shape")
+    for t in (dt_bias, a_log, d_skip):
+        _need(t.dtype == torch.float32 and t.numel() == heads and t.is_contiguous(), "ssd_scan takes float32 vectors of one entry per head")
+    for t, name in ((q_start, "q_start"), (slots, "slots"), (positions, "positions")):
+        _i32(t, name)
+    ptr, slot_stride, half = _state_views(state, state_offset, heads * state_size * vdim, "ssd_scan")
+    _call("llmp_ssd_scan", _ptr(xbc), xbc.stride(0), _ptr(dt), dt.stride(0), _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), ptr,
+          slot_stride, half, _ptr(q_start), _ptr(slots), _ptr(positions), _ptr(y), y.stride(0), slots.numel(), heads, groups,
+          state_size, vdim, _stream())
+    return y
+
+
+def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, group_size: int, eps: float,
+                     gate_first: bool) -> torch.Tensor:
+    """Rows cut into groups of ``group_size`` entries, each divided by its own root mean square. ``gate_first``: out =
+    rms(y silu(gate)) * weight[column]; else out = rms(y) * weight[column within the group] * sigmoid(gate). ``y`` and
+    ``gate`` float32 views, ``weight`` float32."""
+    N, W = y.shape
+    _need(y.dtype == torch.float32 and gate.dtype == torch.float32 and y.stride(1) == 1 and gate.stride(1) == 1 and gate.shape == (N, W),
+          "gated_group_norm takes float32 rows and gates")
+    _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == (W if gate_first else group_size),
+          "gated_group_norm: the weight has the wrong size")
+    _need(out.shape == (N, W) and out.stride(1) == 1, "gated_group_norm: the output has the wrong shape")
+    _call("llmp_gated_group_norm", _ptr(y), y.stride(0), _ptr(gate), gate.stride(0), _ptr(weight), _ptr(out), dtype_code(out.dtype),
+          out.stride(0), N, W, int(group_size), 0 if gate_first else 1, float(eps), _stream())
+    return out
+
+
+def delta_prep(q: torch.Tensor, k: torch.Tensor, decay: torch.Tensor, beta: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+               heads: int, qk_heads: int, dim: int) -> None:
+    """In place, per token (csrc/delta_rule.cu): ``q`` and ``k`` float32 [tokens, qk_heads dim] become unit vectors per head (q also
+    times dim^(-1/2)); ``decay`` float32 [tokens, heads dim] goes from its pre-activation to exp(-exp(a_log[head]) softplus(. +
+    dt_bias)); ``beta`` float32 [tokens, heads] to its sigmoid. All four may be views with a dense last axis."""
+    N = q.shape[0]
+    for t, w, name in ((q, qk_heads * dim, "q"), (k, qk_heads * dim, "k"), (decay, heads * dim, "decay"), (beta, heads, "beta")):
+        _need(t.dtype == torch.float32 and t.stride(1) == 1 and t.shape == (N, w), f"delta_prep: {name} must be float32 [tokens, {w}]")
+    _need(a_log.dtype == torch.float32 and a_log.numel() == heads and a_log.is_contiguous() and dt_bias.dtype == torch.float32 and
+          dt_bias.numel() == heads * dim and dt_bias.is_contiguous(), "delta_prep takes float32 A_log [heads] and dt_bias [heads dim]")
+    _call("llmp_delta_prep", _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(decay), decay.stride(0), _ptr(beta), beta.stride(0),
+          _ptr(a_log), _ptr(dt_bias), N, heads, qk_heads, dim, _stream())
+
+
+def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, beta: torch.Tensor, state: torch.Tensor,
+               state_offset: int, q_start: torch.Tensor, slots: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
+               heads: int, qk_heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """The gated delta rule over the step's tokens, request by request (csrc/delta_rule.cu); inputs as ``delta_prep`` leaves
+    them, ``v`` float32 [tokens, heads vdim], ``out`` float32 [tokens, heads vdim]. The state piece holds two copies of
+    [heads, dim, vdim]."""
+    N = q.shape[0]
+    for t, w, name in ((q, qk_heads * dim, "q"), (k, qk_heads * dim, "k"), (v, heads * vdim, "v"), (decay, heads * dim, "decay"),
+                       (beta, heads, "beta"), (out, heads * vdim, "out")):
+        _need(t.dtype == torch.float32 and t.stride(1) == 1 and t.shape == (N, w), f"delta_scan: {name} must be float32 [tokens, {w}]")
+    for t, name in ((q_start, "q_start"), (slots, "slots"), (positions, "positions")):
+        _i32(t, name)
+    ptr, slot_stride, half = _state_views(state, state_offset, heads * dim * vdim, "delta_scan")
+    _call("llmp_delta_scan", _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(decay), decay.stride(0),
+          _ptr(beta), beta.stride(0), ptr, slot_stride, half, _ptr(q_start), _ptr(slots), _ptr(positions), _ptr(out), out.stride(0),
+          slots.numel(), heads, qk_heads, dim, vdim, _stream())
+    return out
+
+
+def sig_qkv_post(qkv: torch.Tensor, bias: Optional[torch.Tensor], cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                 rotary_dim: int, q_out: torch.Tensor, slot_mapping: Optional[torch.Tensor], pages: Optional[torch.Tensor],
+                 heads: int, kv_heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """After the float32 product [q | k | v] (csrc/sigmoid_attention.cu): bias, rotation of the first ``rotary_dim`` entries of
+    every query and key head (entry i with i + rotary_dim / 2), queries to ``q_out`` [tokens, heads dim], the token's [k | v]
+    rows to its page slot. ``pages``: [pages, kv_heads, page_size, dim + vdim]."""
+    N = qkv.shape[0]
+    width = (heads + kv_heads) * dim + kv_heads * vdim
+    _need(qkv.dtype == torch.float32 and qkv.stride(1) == 1 and qkv.shape[1] == width, "sig_qkv_post takes the float32 product [q | k | v]")
+    _need(bias is None or (bias.numel() == width and bias.is_contiguous()), "sig_qkv_post: the bias has the wrong size")
+    _need(q_out.shape == (N, heads * dim) and q_out.stride(1) == 1, "sig_qkv_post: the query output has the wrong shape")
+    if rotary_dim:
+        _need(cos is not None and sin is not None and cos.dtype == torch.float32 and cos.shape == (N, rotary_dim // 2) and
+              cos.is_contiguous() and sin.is_contiguous(), "sig_qkv_post: the rotation's tables must be float32 [tokens, rotary_dim / 2]")
+    page_size = 0
+    if pages is not None:
+        _need(slot_mapping is not None and pages.dim() == 4 and pages.is_contiguous() and pages.shape[1] == kv_heads and
+              pages.shape[3] == dim + vdim and pages.dtype == q_out.dtype, "sig_qkv_post: pages must be [pages, kv_heads, page_size, dim + vdim] of the queries' type")
+        _i32(slot_mapping, "slot_mapping")
+        page_size = pages.shape[2]
+    _call("llmp_sig_qkv_post", _ptr(qkv), qkv.stride(0), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32, _ptr(cos),
+          _ptr(sin), int(rotary_dim), _ptr(q_out), dtype_code(q_out.dtype), q_out.stride(0), _ptr(slot_mapping) if pages is not None else None,
+          _ptr(pages), page_size, N, heads, kv_heads, dim, vdim, _stream())
+    return q_out
+
+
+SIGMOID_MAX_HEADS = 32             # query heads whose weights one block of the sigmoid attention kernel mixes
+SIGMOID_SEGMENT_KEYS = 1024       # keys of a segment when a token's keys are shared among blocks (a multiple of the key tile)
+
+
+def sigmoid_attention(q: torch.Tensor, pages: torch.Tensor, tables: torch.Tensor, token_request: torch.Tensor, positions: torch.Tensor,
+                      talk: torch.Tensor, head_bias: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int,
+                      scale: float, softcap: float, segments: int = 1) -> torch.Tensor:
+    """Causal attention whose weights are sigmoid(capped score + head_bias[head]), mixed across heads by ``talk`` [heads, heads]
+    before they meet the values, not normalised over keys (csrc/sigmoid_attention.cu). ``segments`` > 1: a token's keys are
+    shared among that many blocks in fixed ranges of ``SIGMOID_SEGMENT_KEYS`` and the partial sums added in their order."""
+    N = q.shape[0]
+    _need(q.shape == (N, heads * dim) and q.stride(1) == 1 and out.shape == (N, heads * vdim) and out.stride(1) == 1 and
+          q.dtype == out.dtype == pages.dtype, "sigmoid_attention: queries, pages and output must have one type and matching shapes")
+    _need(pages.dim() == 4 and pages.is_contiguous() and pages.shape[1] == kv_heads and pages.shape[3] == dim + vdim,
+          "sigmoid_attention: pages must be [pages, kv_heads, page_size, dim + vdim]")
+    _need(talk.dtype == torch.float32 and talk.is_contiguous() and talk.shape == (heads, heads) and head_bias.dtype == torch.float32 and
+          head_bias.is_contiguous() and head_bias.numel() == heads, "sigmoid_attention takes a float32 head mix [heads, heads] and bias [heads]")
+    _need(tables.dtype == torch.int32 and tables.dim() == 2 and tables.stride(1) == 1, "block tables must be int32 [requests, width]")
+    _need(tables.is_contiguous(), "block tables must be contiguous")
+    _i32(token_request, "token_request")
+    _i32(positions, "positions")
+    partial = None
+    if segments > 1:
+        partial = torch.empty((N, segments, heads * vdim), dtype=torch.float32, device=q.device)
+    _call("llmp_sigmoid_attention", _ptr(q), q.stride(0), _ptr(pages), dtype_code(q.dtype), _ptr(tables), tables.shape[1],
+          _ptr(token_request), _ptr(positions), _ptr(talk), _ptr(head_bias), _ptr(out), out.stride(0), _ptr(partial), int(segments),
+          SIGMOID_SEGMENT_KEYS, N, heads, kv_heads, dim, vdim, pages.shape[2], float(scale), float(softcap or 0.0), _stream())
+    return out
+
+
+def xielu(z: torch.Tensor, bias: Optional[torch.Tensor], a_pos: float, a_neg: float, out: torch.Tensor) -> torch.Tensor:
+    """out = f(z + bias) with f(v) = a_pos v^2 + v / 2 for v > 0 and a_neg (exp(v) - 1 - v) + v / 2 otherwise; ``z`` float32."""
+    N, F = z.shape
+    _need(z.dtype == torch.float32 and z.is_contiguous() and out.is_contiguous() and out.shape == (N, F), "xielu takes dense float32 rows")
+    _need(bias is None or (bias.numel() == F and bias.is_contiguous()), "xielu: the bias has the wrong size")
+    _call("llmp_xielu", _ptr(z), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32, float(a_pos), float(a_neg), _ptr(out),
+          dtype_code(out.dtype), N, F, _stream())
+    return out
+
+
+def scaled_sum(a: torch.Tensor, scale_a: float, b: torch.Tensor, scale_b: float, out: torch.Tensor) -> torch.Tensor:
+    """out = scale_a a + scale_b b, all float32 and dense."""
+    _need(a.dtype == b.dtype == out.dtype == torch.float32 and a.is_contiguous() and b.is_contiguous() and out.is_contiguous() and
+          a.shape == b.shape == out.shape, "scaled_sum takes dense float32 tensors of one shape")
+    _call("llmp_scaled_sum", _ptr(a), float(scale_a), _ptr(b), float(scale_b), _ptr(out), a.numel(), _stream())
     return out

@@ -106,3 +106,48 @@ class ReluSquaredMLP(FeedForward):
         z = linear(x, self.w_up)
         kernels.relu_squared(z, z)
         return linear(z, self.w_down, out_dtype=torch.float32), None
+
+
+@register_feed_forward("xielu_mlp")
+class XieluMLP(FeedForward):
+    """``down(f(up(x) + b_up)) + b_down`` without gate, with the piecewise activation
+
+        f(z) = a_pos z^2 + z / 2                       for z > 0
+        f(z) = a_neg (exp(z) - 1 - z) + z / 2          for z <= 0
+
+    whose two coefficients are learned as ``act = (p, q)``: a_pos = softplus(p), a_neg = 1/2 + softplus(q) (both
+    branches have slope 1/2 at zero). The first product leaves float32, bias and activation are float32
+    (``csrc/activations.cu``), the activation is rounded once to the compute type for the down product, whose result is
+    float32. ``bias``: whether the two projections have biases (``<name>.b``)."""
+
+    graph_safe = True
+
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, bias: bool = True):
+        self.prefix, self.hidden_size, self.intermediate_size, self.bias = prefix, int(hidden_size), int(intermediate_size), bool(bias)
+        self.w_up = self.w_down = self.b_up = self.b_down = None
+        self.a_pos = self.a_neg = 0.0
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        p, H, I = self.prefix, self.hidden_size, self.intermediate_size
+        specs = {f"{p}.up": ParamSpec((I, H)), f"{p}.down": ParamSpec((H, I)), f"{p}.act": ParamSpec((2,), role="vector", init="unit")}
+        if self.bias:
+            specs.update({f"{p}.up.b": ParamSpec((I,), role="vector", init="small"),
+                          f"{p}.down.b": ParamSpec((H,), role="vector", init="small")})
+        return specs
+
+    def load(self, get: TensorGetter) -> None:
+        p = self.prefix
+        self.w_up = get(f"{p}.up", "matrix").contiguous()
+        self.w_down = get(f"{p}.down", "matrix").contiguous()
+        if self.bias:
+            self.b_up = get(f"{p}.up.b", "vector").float().contiguous()
+            self.b_down = get(f"{p}.down.b", "vector").float().contiguous()
+        # softplus in float64 on the host: the two numbers are constants of the layer from here on
+        act = torch.nn.functional.softplus(get(f"{p}.act", "vector").double().cpu())
+        self.a_pos, self.a_neg = float(act[0]), 0.5 + float(act[1])
+
+    def forward(self, x, ctx):
+        z = linear(x, self.w_up, out_dtype=torch.float32)
+        act = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
+        kernels.xielu(z, self.b_up, self.a_pos, self.a_neg, act)
+        return linear(act, self.w_down, out_dtype=torch.float32), self.b_down

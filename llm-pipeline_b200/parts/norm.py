@@ -22,10 +22,11 @@ from .registry import register_norm
 class RMSNorm(Norm):
     graph_safe = True
 
-    def __init__(self, prefix: str, size: int, eps: float, offset: float = 0.0, name: Optional[str] = None):
+    def __init__(self, prefix: str, size: int, eps: float, offset: float = 0.0, name: Optional[str] = None, gain: float = 1.0):
         """``offset``: the stored weight w stands for ``offset + w`` (1.0 for weights kept around zero); ``name``: the
-        tensor's full name where it is not ``<prefix>.weight``."""
-        self.prefix, self.size, self.eps, self.offset = prefix, int(size), float(eps), float(offset)
+        tensor's full name where it is not ``<prefix>.weight``; ``gain``: a constant factor on the normed rows (a layer
+        that adds ``m * norm(sublayer)`` to its residual gives that norm the gain m)."""
+        self.prefix, self.size, self.eps, self.offset, self.gain = prefix, int(size), float(eps), float(offset), float(gain)
         self.name = name or f"{prefix}.weight"
         self.weight: Optional[torch.Tensor] = None
 
@@ -34,8 +35,8 @@ class RMSNorm(Norm):
 
     def load(self, get: TensorGetter) -> None:
         self.weight = get(self.name, "vector").contiguous()
-        if self.offset:
-            self.weight = (self.weight.float() + self.offset).contiguous()      # the factor itself, float32
+        if self.offset or self.gain != 1.0:
+            self.weight = ((self.weight.float() + self.offset) * self.gain).contiguous()      # the factor itself, float32
 
     def add_norm(self, stream: ResidualStream, ctx, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         count = rows.numel() if rows is not None else stream.residual.shape[0]

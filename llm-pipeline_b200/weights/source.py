@@ -140,7 +140,9 @@ class RandomSource(WeightSource):
 
     def __init__(self, expected: Dict[str, ParamSpec], seed: int, std: float = 0.02,
                  dtype: torch.dtype = torch.bfloat16, device: str = "cpu"):
-        self.expected = {n: s for n, s in expected.items() if not s.optional}
+        self.expected = {n: (s if None not in s.shape else ParamSpec(
+            tuple(FREE_DIMENSION_DEFAULT if d is None else d for d in s.shape), s.role, s.optional, s.init))
+            for n, s in expected.items() if not s.optional}
         self.seed, self.std, self.dtype, self.device = int(seed), float(std), dtype, torch.device(device)
 
     def names(self):
@@ -169,6 +171,16 @@ class RandomSource(WeightSource):
         return value.to(self.dtype)
 
 
+FREE_DIMENSION_DEFAULT = 8     # what the random-weights mode takes for a size that only the tensor gives
+
+
+def shape_matches(stored, expected) -> bool:
+    """Whether a stored shape is the expected one; an expected size of None is given by the tensor itself (an inner
+    size of a two-step projection that no configuration key names)."""
+    stored, expected = tuple(stored), tuple(expected)
+    return len(stored) == len(expected) and all(e is None or int(s) == int(e) for s, e in zip(stored, expected))
+
+
 def check_names_and_shapes(expected: Dict[str, ParamSpec], source: WeightSource,
                            ignorable: Iterable[str] = ()) -> None:
     """Raise one ``WeightError`` that lists all missing, unexpected and mis-shaped tensors."""
@@ -178,7 +190,7 @@ def check_names_and_shapes(expected: Dict[str, ParamSpec], source: WeightSource,
     unexpected = sorted(n for n in have if n not in expected and n not in ignorable
                         and not n.endswith(IGNORED_SUFFIXES))
     wrong = [(n, source.shape(n), tuple(s.shape)) for n, s in expected.items()
-             if n in have and tuple(source.shape(n)) != tuple(s.shape)]
+             if n in have and not shape_matches(source.shape(n), s.shape)]
     if missing or unexpected or wrong:
         raise WeightError(missing, unexpected, wrong)
 
