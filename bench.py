@@ -30,6 +30,9 @@ time of every kernel class of both, in one JSON line of its own shape.
 ``--compare razelorn [--size 1k|2k]`` does the same for the Razelorn decoder (differential attention under a sliding
 window beside a dense or routed-expert feed-forward on one layer norm).
 
+``--compare nufolix [--size 1k|2k]`` does the same for the Nufolix decoder (a state-space mixer; sigmoid attention with
+mixed heads side by side with a gated delta rule; dense xIELU feed-forwards).
+
 ``--impl reference`` runs DavidAkinpelu/llm-pipeline's own ``Qwen3ForCausalLM`` from
 ``baseline/_ref`` (installed offline with pip --no-deps --target) with its ``past_key_values``
 loop at the same sizes and prints the same line with ``"impl": "reference"``.
@@ -799,10 +802,68 @@ def razelorn_work(z, tokens, keys_per_token, decode):
     return work
 
 
+# ``--compare nufolix``: the same two measurements for the Nufolix decoder: four layers (a state-space mixer alone, then
+# sigmoid attention with mixed heads side by side with a gated delta rule and a dense xIELU feed-forward, twice) beside a
+# Qwen3 dense decoder of the same width, depth and vocabulary.
+NUFOLIX_SIZES = {
+    "1k": {"width": 1024, "ssd_heads": 16, "ssd_vdim": 128, "state": 64, "groups": 1, "norm_groups": 1, "conv": 4,
+           "heads": 8, "kv_heads": 4, "dim": 128, "vdim": 128, "rot": 64, "delta_heads": 8, "delta_qk_heads": 8, "delta_dim": 64,
+           "delta_vdim": 128, "ff": 4096, "layers": 4, "vocab": 32000, "qwen_heads": (8, 4)},
+    "2k": {"width": 2048, "ssd_heads": 32, "ssd_vdim": 128, "state": 128, "groups": 1, "norm_groups": 1, "conv": 4,
+           "heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "rot": 64, "delta_heads": 16, "delta_qk_heads": 16, "delta_dim": 128,
+           "delta_vdim": 128, "ff": 8192, "layers": 4, "vocab": 32000, "qwen_heads": (16, 8)},
+}
+
+
+def nufolix_config(z):
+    ssd = {"heads": z["ssd_heads"], "vdim": z["ssd_vdim"], "state": z["state"], "groups": z["groups"], "conv": z["conv"],
+           "norm_groups": z["norm_groups"]}
+    side = {"left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+                     "softcap": 30.0, "rot": {"base": 10000.0, "dims": z["rot"]}},
+            "right": {"heads": z["delta_heads"], "kv_heads": z["delta_qk_heads"], "dim": z["delta_dim"], "vdim": z["delta_vdim"],
+                      "conv": z["conv"]},
+            "left_scale": 1.0, "right_scale": 1.0}
+    layers = []
+    for i in range(z["layers"]):
+        if i % 2 == 0:
+            layers.append({"type": "mamba2", "mixer": ssd, "mlp": None})
+        else:
+            layers.append({"type": "parallel", "mixer": side, "mlp": {"kind": "dense", "ff": z["ff"]}})
+    return {"architecture": "Nufolix", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "residual_mult": 1.0,
+            "embedding": {"scale": 1.0}, "layers": layers}
+
+
+def nufolix_work(z, tokens, keys_per_token, decode, requests=1):
+    """Closed-form work of the design's own kernel classes for one step: label -> (bytes, flops)."""
+    L = z["layers"]
+    ssd_layers, side_layers = (L + 1) // 2, L // 2
+    Hs, P, Ns, Gs = z["ssd_heads"], z["ssd_vdim"], z["state"], z["groups"]
+    H, G, d, dv = z["heads"], z["kv_heads"], z["dim"], z["vdim"]
+    Hd, Gd, dd, ddv = z["delta_heads"], z["delta_qk_heads"], z["delta_dim"], z["delta_vdim"]
+    ssd_channels = Hs * P + 2 * Gs * Ns
+    delta_channels = 2 * Gd * dd + Hd * ddv
+    work = {}
+    # rows in and out in float32; the state of every request read and written once a step
+    work["short_conv"] = ((ssd_layers * ssd_channels + side_layers * delta_channels) * tokens * 8, 0.0)
+    work["ssd_scan"] = (ssd_layers * (tokens * (ssd_channels + Hs + Hs * P) * 4 + requests * Hs * Ns * P * 8), 0.0)
+    work["delta_scan"] = (side_layers * (tokens * (delta_channels + Hd * dd + Hd + Hd * ddv) * 4 + requests * Hd * dd * ddv * 8), 0.0)
+    work["delta_prep"] = (side_layers * tokens * (2 * Gd * dd + Hd * dd + Hd) * 8, 0.0)
+    work["gated_group_norm"] = ((ssd_layers * Hs * P + side_layers * Hd * ddv) * tokens * (4 + 4 + 2), 0.0)
+    work["sig_qkv_post"] = (side_layers * tokens * ((H + G) * d + G * dv) * (4 + 2), 0.0)
+    work["xielu"] = (side_layers * tokens * z["ff"] * (4 + 2), 0.0)
+    if decode:
+        work["sigmoid_attention"] = (side_layers * tokens * keys_per_token * G * (d + dv) * 2, 0.0)
+    else:
+        work["sigmoid_attention"] = (0.0, side_layers * 2.0 * tokens * keys_per_token * H * (d + dv))
+    work["sigmoid_attention_mma"] = work["sigmoid_attention"]
+    return work
+
+
 def run_compare(args):
     peak = peaks()
     sizes, config_of, work_of = {"zupilorn": (ZUPILORN_SIZES, zupilorn_config, zupilorn_work),
-                                 "razelorn": (RAZELORN_SIZES, razelorn_config, razelorn_work)}[args.compare]
+                                 "razelorn": (RAZELORN_SIZES, razelorn_config, razelorn_work),
+                                 "nufolix": (NUFOLIX_SIZES, nufolix_config, lambda z, n, k, d: nufolix_work(z, n, k, d, args.batch if d else 1))}[args.compare]
     z = sizes[args.size]
     clocks = ClockSampler()
     clocks.start()
@@ -898,7 +959,7 @@ def main() -> int:
     parser.add_argument("--lean", action="store_true", help="leave out the per-kernel breakdown, the page-size point, the plain "
                         "PyTorch baseline and the self-check")
     parser.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per page of the key/value cache")
-    parser.add_argument("--compare", default="", choices=("", "zupilorn", "razelorn"),
+    parser.add_argument("--compare", default="", choices=("", "zupilorn", "razelorn", "nufolix"),
                         help="instead of the headline: prefill and decode of this design at real layer sizes beside a Qwen3 dense "
                         "decoder of the same width and depth, with the time of every kernel class")
     parser.add_argument("--size", default="2k", choices=tuple(ZUPILORN_SIZES), help="with --compare: the layer sizes")
