@@ -84,6 +84,7 @@ _SIGNATURES = {
     "llmp_delta_scan": [_P, _L, _P, _L, _P, _L, _P, _L, _P, _L, _P, _L, _L, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _P],
     "llmp_sig_qkv_post": [_P, _L, _P, _I, _P, _P, _I, _P, _I, _L, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "llmp_sigmoid_attention": [_P, _L, _P, _I, _P, _I, _P, _P, _P, _P, _P, _L, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P],
+    "llmp_sigmoid_attention_mma": [_P, _L, _P, _P, _I, _P, _P, _P, _P, _P, _I, _P, _P, _P, _L, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P],
     "llmp_xielu": [_P, _P, _I, _F, _F, _P, _I, _L, _I, _P],
     "llmp_scaled_sum": [_P, _F, _P, _F, _P, _L, _P],
 }
@@ -1302,6 +1303,8 @@ def sig_qkv_post(qkv: torch.Tensor, bias: Optional[torch.Tensor], cos: Optional[
 
 SIGMOID_MAX_HEADS = 32             # query heads whose weights one block of the sigmoid attention kernel mixes
 SIGMOID_SEGMENT_KEYS = 1024       # keys of a segment when a token's keys are shared among blocks (a multiple of the key tile)
+SIGMOID_MMA_SEGMENT_KEYS = 128    # the same for the tensor-core kernel, whose blocks walk a tile of keys for up to 16 tokens at once
+SIGMOID_MMA_ROWS = 16             # new tokens of a request in a tile of the tensor-core kernel
 
 
 def sigmoid_attention(q: torch.Tensor, pages: torch.Tensor, tables: torch.Tensor, token_request: torch.Tensor, positions: torch.Tensor,
@@ -1327,6 +1330,44 @@ def sigmoid_attention(q: torch.Tensor, pages: torch.Tensor, tables: torch.Tensor
     _call("llmp_sigmoid_attention", _ptr(q), q.stride(0), _ptr(pages), dtype_code(q.dtype), _ptr(tables), tables.shape[1],
           _ptr(token_request), _ptr(positions), _ptr(talk), _ptr(head_bias), _ptr(out), out.stride(0), _ptr(partial), int(segments),
           SIGMOID_SEGMENT_KEYS, N, heads, kv_heads, dim, vdim, pages.shape[2], float(scale), float(softcap or 0.0), _stream())
+    return out
+
+
+def sigmoid_attention_mma_supports(dtype: torch.dtype, heads: int, kv_heads: int, dim: int, vdim: int) -> bool:
+    """Whether the tensor-core kernel has an instance for these sizes (bfloat16, up to 16 heads, head sizes 16, 32, 64, 96 or 128)."""
+    if dtype != torch.bfloat16:
+        return False
+    fn = library().llmp_sigmoid_attention_mma_supports
+    fn.argtypes = [_I, _I, _I, _I]
+    fn.restype = ctypes.c_int
+    return bool(fn(int(heads), int(kv_heads), int(dim), int(vdim)))
+
+
+def sigmoid_attention_mma(q: torch.Tensor, pages: torch.Tensor, tables: torch.Tensor, q_start: torch.Tensor, ctx_len: torch.Tensor,
+                          positions: torch.Tensor, tile_req: torch.Tensor, tile_tok0: torch.Tensor, talk: torch.Tensor,
+                          head_bias: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int, scale: float,
+                          softcap: float, segments: int = 1) -> torch.Tensor:
+    """``sigmoid_attention`` on the tensor cores for bfloat16 (csrc/sigmoid_attention_mma.cu). ``tile_req``/``tile_tok0``: the
+    work list (request and first new token of every tile of ``SIGMOID_MMA_ROWS`` tokens), in the order of the keys a tile
+    sees. ``segments`` > 1: fixed ranges of ``SIGMOID_MMA_SEGMENT_KEYS`` keys go to blocks of their own."""
+    N = q.shape[0]
+    _need(q.dtype == out.dtype == pages.dtype == torch.bfloat16 and q.shape == (N, heads * dim) and q.stride(1) == 1 and
+          out.shape == (N, heads * vdim) and out.stride(1) == 1, "sigmoid_attention_mma takes bfloat16 queries, pages and output of matching shapes")
+    _need(pages.dim() == 4 and pages.is_contiguous() and pages.shape[1] == kv_heads and pages.shape[3] == dim + vdim,
+          "sigmoid_attention_mma: pages must be [pages, kv_heads, page_size, dim + vdim]")
+    _need(talk.dtype == torch.float32 and talk.is_contiguous() and talk.shape == (heads, heads) and head_bias.dtype == torch.float32 and
+          head_bias.is_contiguous() and head_bias.numel() == heads, "sigmoid_attention_mma takes a float32 head mix [heads, heads] and bias [heads]")
+    _need(tables.dtype == torch.int32 and tables.dim() == 2 and tables.is_contiguous(), "block tables must be dense int32 [requests, width]")
+    for t, name in ((q_start, "q_start"), (ctx_len, "ctx_len"), (positions, "positions"), (tile_req, "tile_req"), (tile_tok0, "tile_tok0")):
+        _i32(t, name)
+    _need(tile_req.numel() == tile_tok0.numel(), "sigmoid_attention_mma: the work list's columns differ in length")
+    partial = None
+    if segments > 1:
+        partial = torch.empty((N, segments, heads * vdim), dtype=torch.float32, device=q.device)
+    _call("llmp_sigmoid_attention_mma", _ptr(q), q.stride(0), _ptr(pages), _ptr(tables), tables.shape[1], _ptr(q_start), _ptr(ctx_len),
+          _ptr(positions), _ptr(tile_req), _ptr(tile_tok0), tile_req.numel(), _ptr(talk), _ptr(head_bias), _ptr(out), out.stride(0),
+          _ptr(partial), int(segments), SIGMOID_MMA_SEGMENT_KEYS, N, heads, kv_heads, dim, vdim, pages.shape[2], float(scale),
+          float(softcap or 0.0), _stream())
     return out
 
 

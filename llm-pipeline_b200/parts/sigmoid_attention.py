@@ -13,7 +13,10 @@ The three projections are one product against [Wq; Wk; Wv] with a float32 result
 writes the queries in the compute type and the token's [k | v] rows into its page slot; the attention kernel reads all
 keys and values from pages, this step's included. Scores, weights, their mix and the weighted sums are float32
 (``csrc/sigmoid_attention.cu``). Because no sum over keys normalises anything, ranges of keys add up: steps with few
-tokens over long contexts give every fixed range of keys a block of its own."""
+tokens over long contexts give every fixed range of keys a block of its own. In bfloat16, for the head counts and sizes
+it has instances of, the tensor-core kernel (``csrc/sigmoid_attention_mma.cu``) takes prompts and single tokens alike:
+tiles of up to 16 new tokens of a request, scores and values on mma.sync, the weights and their mix in float32, the mixed
+weights rounded to bfloat16 for the product with the values."""
 
 from __future__ import annotations
 
@@ -25,6 +28,7 @@ from ..cache.spec import HeadRowPagesSpec
 from ..ops import kernels
 from ..ops.linear import linear
 from ..weights.source import ParamSpec
+from .attention import AttentionPolicy
 from .base import LayerCache, Mixer, TensorGetter
 from .registry import register_mixer
 
@@ -35,6 +39,8 @@ class SigmoidAttention(Mixer):
 
     # Blocks per SM below which a step's tokens are too few to fill the GPU and the keys are cut into segments.
     SEGMENTS_BELOW_BLOCKS_PER_SM = 2.0
+    MMA_SEGMENTS_BELOW_BLOCKS_PER_SM = 0.5      # the same for the tensor-core kernel, a block of which fills an SM
+    SEGMENTS_MAX_BYTES = 256 << 20              # the float32 partial sums of all segments never take more than this
 
     def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float,
                  softcap: Optional[float] = None, bias: bool = True, head_mix: bool = True, head_bias: bool = True,
@@ -58,6 +64,8 @@ class SigmoidAttention(Mixer):
         self.names = {n: n for n in ("q", "k", "v", "o", "talk", "pb")}
         self.names.update(names or {})
         self.w_qkv = self.b_qkv = self.w_o = self.talk = self.pb = None
+        self.compute_dtype = None      # the type of the queries and pages, known once the weights are loaded
+        self._mma = None               # whether the tensor-core kernel takes this mixer's sizes in that type
 
     def cache_spec(self) -> HeadRowPagesSpec:
         return HeadRowPagesSpec(self.num_kv_heads, self.dim + self.vdim, None)
@@ -70,9 +78,35 @@ class SigmoidAttention(Mixer):
         return self._segments(shape.num_requests, shape.longest)
 
     def _segments(self, tokens: int, longest: int) -> int:
-        if tokens >= self.SEGMENTS_BELOW_BLOCKS_PER_SM * kernels.sm_count() or longest <= kernels.SIGMOID_SEGMENT_KEYS:
+        if self._mma is None:
+            self._mma = kernels.sigmoid_attention_mma_supports(self.compute_dtype, self.num_heads, self.num_kv_heads, self.dim, self.vdim)
+        blocks, keys, below = tokens, kernels.SIGMOID_SEGMENT_KEYS, self.SEGMENTS_BELOW_BLOCKS_PER_SM
+        if self._mma:
+            # a lower bound of the tiles (a request's last tile may be short); single tokens give exactly one tile each
+            blocks, keys, below = -(-tokens // kernels.SIGMOID_MMA_ROWS), kernels.SIGMOID_MMA_SEGMENT_KEYS, self.MMA_SEGMENTS_BELOW_BLOCKS_PER_SM
+        if blocks >= below * kernels.sm_count() or longest <= keys:
             return 1
-        return -(-longest // kernels.SIGMOID_SEGMENT_KEYS)
+        segments = -(-longest // keys)
+        if tokens * segments * self.num_heads * self.vdim * 4 > self.SEGMENTS_MAX_BYTES:
+            return 1
+        return segments
+
+    def _tiles(self, ctx):
+        key = ("sigmoid_attention_tiles", kernels.SIGMOID_MMA_ROWS)
+        tiles = ctx.memo.get(key)
+        if tiles is None:
+            if ctx.max_q_len == 1:
+                # one token a request: tile r is request r (made on the device, so that a captured step holds no copy from the host)
+                tiles = (torch.arange(ctx.num_requests, dtype=torch.int32, device=ctx.device),
+                         torch.zeros(ctx.num_requests, dtype=torch.int32, device=ctx.device))
+            else:
+                req, tok0, _seg, _slot, _places = AttentionPolicy.plan_items(ctx.starts, ctx.q_lens, kernels.SIGMOID_MMA_ROWS, 0, 1, 1,
+                                                                             kernels.sm_count())
+                host = torch.tensor([req, tok0], dtype=torch.int32).pin_memory()
+                dev = host.to(ctx.device, non_blocking=True)
+                tiles = (dev[0].contiguous(), dev[1].contiguous())
+            ctx.memo[key] = tiles
+        return tiles
 
     def _name(self, key: str) -> str:
         return f"{self.prefix}.{self.names[key]}"
@@ -94,6 +128,7 @@ class SigmoidAttention(Mixer):
         self.w_qkv = torch.cat([get(self._name(n), "matrix") for n in ("q", "k", "v")], dim=0).contiguous()
         self.w_o = get(self._name("o"), "matrix").contiguous()
         device = self.w_o.device
+        self.compute_dtype, self._mma = self.w_o.dtype, None
         if self.bias:
             self.b_qkv = torch.cat([get(self._name(n) + ".b", "vector").float() for n in ("q", "k", "v")]).contiguous()
         self.talk = (get(self._name("talk"), "vector").float().contiguous() if self.head_mix
@@ -114,6 +149,12 @@ class SigmoidAttention(Mixer):
                              cache.pages if cache.writes else None, self.num_heads, self.num_kv_heads, self.dim, self.vdim)
         out = torch.empty((N, self.num_heads * self.vdim), dtype=x.dtype, device=x.device)
         segments = self._segments(N, ctx.decode_ctx_bound or ctx.max_ctx_len)
-        kernels.sigmoid_attention(q, cache.pages, ctx.block_tables[cache.group], ctx.token_request, ctx.positions, self.talk, self.pb,
-                                  out, self.num_heads, self.num_kv_heads, self.dim, self.vdim, self.scale, self.softcap, segments)
+        sizes = (self.num_heads, self.num_kv_heads, self.dim, self.vdim, self.scale, self.softcap, segments)
+        if self._mma and q.dtype == torch.bfloat16:
+            tile_req, tile_tok0 = self._tiles(ctx)
+            kernels.sigmoid_attention_mma(q, cache.pages, ctx.block_tables[cache.group], ctx.q_start, ctx.ctx_len, ctx.positions,
+                                          tile_req, tile_tok0, self.talk, self.pb, out, *sizes)
+        else:
+            kernels.sigmoid_attention(q, cache.pages, ctx.block_tables[cache.group], ctx.token_request, ctx.positions, self.talk,
+                                      self.pb, out, *sizes)
         return linear(out, self.w_o, out_dtype=torch.float32), None

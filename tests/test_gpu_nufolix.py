@@ -216,11 +216,27 @@ def _sigmoid_attention_case(dtype, heads, kv_heads, dim, vdim, n, page, seed, ca
         kernels.sigmoid_attention(qd, pd, table, torch.zeros(n, dtype=torch.int32, device=dev), positions, talk.to(dev), pb.to(dev), out,
                                   heads, kv_heads, dim, vdim, scale, cap, count)
         results[f"{count} segments"] = out.float().cpu()
+    if kernels.sigmoid_attention_mma_supports(dtype, heads, kv_heads, dim, vdim):
+        # the tensor-core kernel: the whole prompt in tiles of 16 tokens, its keys in one block and in ranges; then only the
+        # last 37 tokens as a portion (three tiles, the last one short, the first one starting in the middle of a page)
+        rows = kernels.SIGMOID_MMA_ROWS
+        ctx_len = torch.tensor([n], dtype=torch.int32, device=dev)
+        for tail, count in ((n, 1), (n, -(-n // kernels.SIGMOID_MMA_SEGMENT_KEYS)), (37, 1), (37, -(-n // kernels.SIGMOID_MMA_SEGMENT_KEYS))):
+            out = torch.empty(tail, heads * vdim, device=dev, dtype=dtype)
+            tok0 = torch.arange(0, tail, rows, dtype=torch.int32, device=dev)
+            kernels.sigmoid_attention_mma(qd[n - tail:], pd, table, torch.tensor([0, tail], dtype=torch.int32, device=dev), ctx_len,
+                                          positions[n - tail:].contiguous(), torch.zeros_like(tok0), tok0, talk.to(dev), pb.to(dev), out,
+                                          heads, kv_heads, dim, vdim, scale, cap, count)
+            full = torch.zeros(n, heads * vdim)
+            full[n - tail:] = out.float().cpu()
+            full[:n - tail] = want[:n - tail].float()
+            results[f"tensor cores, last {tail} tokens, {count} key ranges"] = full
     return results, want
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("sizes", [(4, 2, 16, 24, 0.0), (3, 3, 12, 20, 2.0), (6, 1, 48, 48, 8.0), (2, 2, 128, 64, 0.0), (32, 2, 16, 16, 30.0),
+@pytest.mark.parametrize("sizes", [(4, 2, 16, 24, 0.0), (3, 3, 12, 20, 2.0), (6, 1, 48, 48, 8.0), (2, 2, 128, 64, 0.0), (32, 2, 16, 16, 30.0), (4, 2, 16, 32, 0.0), (6, 3, 96, 64, 5.0),
+                                   (16, 4, 128, 128, 3.0), (12, 12, 32, 96, 0.0),
                                    (1, 1, 64, 128, 1.0), (5, 5, 10, 200, 0.0)], ids=str)
 def test_sigmoid_attention_alone(dtype, sizes):
     """Weights that are sigmoids of capped scores, mixed across heads, not normalised: grouped heads, values of another
