@@ -8,9 +8,9 @@
 //
 // delta_prep (a block per token, in place): q and k become unit vectors per head, x / sqrt(sum(x^2) + 1e-6), q also
 // times d^(-1/2); the decay's pre-activation becomes exp(-exp(A_log[h]) * softplus(pre + dt_bias)); beta's becomes its
-// sigmoid. delta_scan: a block owns (request, head) and walks the request's tokens in order; thread (j, r) holds rows
-// r, r + R, .. of column j in registers. The state lives in the request's slot as two copies that take turns by the
-// parity of the last position written. Everything is float32.
+// sigmoid. delta_scan: a block owns (request, head, a range of value columns) and walks the request's tokens in order;
+// lane (j, r) holds rows r, r + R, .. of column j in registers. The state lives in the request's slot as two copies that
+// take turns by the parity of the last position written. Everything is float32.
 #include "common.cuh"
 
 namespace {
@@ -54,20 +54,55 @@ struct DeltaArgs {
     int H, G, d, dv;
 };
 
-template <int NT>
-__global__ void delta_scan_kernel(const DeltaArgs a) {
-    extern __shared__ float smem[];
+constexpr int DS_THREADS = 128;   // threads of a block that hold the state; one more warp copies the inputs
+constexpr int DS_STAGES = 3;      // stages of the input ring
+
+__device__ __forceinline__ void ds_cp_async_4(float* smem_dst, const float* gmem_src) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void ds_cp_async_16(float* smem_dst, const float* gmem_src) {
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+// `n` floats from global to shared memory by the lanes of one warp, in 16-byte pieces where `vec` says both are aligned
+__device__ __forceinline__ void ds_copy_row(float* dst, const float* src, int n, bool vec, int lane) {
+    if (vec) for (int e = lane * 4; e < n; e += 128) ds_cp_async_16(dst + e, src + e);
+    else for (int e = lane; e < n; e += 32) ds_cp_async_4(dst + e, src + e);
+}
+
+template <int V> struct DsVec { float v[V]; };
+template <int V> __device__ __forceinline__ DsVec<V> ds_load(const float* p) {
+    DsVec<V> r;
+    if constexpr (V == 4) { const float4 t = *reinterpret_cast<const float4*>(p); r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w; }
+    else if constexpr (V == 2) { const float2 t = *reinterpret_cast<const float2*>(p); r.v[0] = t.x; r.v[1] = t.y; }
+    else r.v[0] = *p;
+    return r;
+}
+
+// A block owns (request, head, a range of value columns); the columns of the state never meet, so nothing passes
+// between blocks. Within a warp, R consecutive lanes share a column: lane (column, r) holds NT state rows of its column
+// in registers, in runs of V = min(NT, 4) rows (run i of lane r: rows (i R + r) V ..), so that a lane reads its keys,
+// queries and decays as 16-byte words and the lanes of a column read consecutive words; rows past d are zeros that
+// stay zeros. The sums over rows are rounds of shuffles. A fifth warp copies the tokens' inputs through a ring of
+// DS_STAGES stages of `stage_tokens` tokens (cp.async, 16 bytes where the rows allow it), so a block synchronises once
+// per stage, not per token, and the warps that hold the state do no address arithmetic for the copies.
+template <int NT, int R>
+__global__ void __launch_bounds__(DS_THREADS + 32) delta_scan_kernel(const DeltaArgs a, const int stage_tokens, const int vec) {
+    extern __shared__ __align__(16) float smem[];
+    constexpr int V = NT < 4 ? NT : 4;
+    constexpr int DP = NT * R;                           // rows with padding
+    constexpr int COLS = DS_THREADS / R;                 // columns of a block
+    constexpr int ROW = 3 * DP + COLS + 4;               // k, q, decay (padded), the block's columns of v, beta
     const int r = blockIdx.x, h = blockIdx.y;
     const int begin = a.q_start[r], end = a.q_start[r + 1];
     if (end <= begin) return;
     const int d = a.d, dv = a.dv;
-    const int R = blockDim.x / dv;
-    const int j = threadIdx.x % dv, rr = threadIdx.x / dv;
-    const bool owner = rr < R;
-    const int row = 3 * d + dv;                          // k, q, decay, v of a token
-    float* buf = smem;                                   // [2][row]
-    float* part = smem + 2 * row;                        // [R][2 dv + 1]: S^T k, S^T q, k . q
-    const int ps = 2 * dv + 1;
+    const bool loader = threadIdx.x >= DS_THREADS;
+    const int lane = threadIdx.x & 31;
+    const int rr = threadIdx.x % R, col = (threadIdx.x / R) % COLS;
+    const int j0 = blockIdx.z * COLS, j = j0 + col;
+    const bool valid = !loader && j < dv;
     const int g = h / (a.H / a.G);
     const int p0 = a.positions[begin];
     float* slot = a.state + (size_t)a.slots[r] * a.state_slot + (size_t)h * d * dv;
@@ -76,60 +111,81 @@ __global__ void delta_scan_kernel(const DeltaArgs a) {
     float S[NT];
 #pragma unroll
     for (int i = 0; i < NT; ++i) {
-        const int c = rr + i * R;
-        S[i] = (owner && c < d) ? rd[(size_t)c * dv + j] : 0.f;
+        const int c = ((i / V) * R + rr) * V + i % V;
+        S[i] = (valid && c < d) ? rd[(size_t)c * dv + j] : 0.f;
     }
-    auto fetch = [&](int t, float* dst) {
-        const float* kr = a.k + (size_t)t * a.k_t + (size_t)g * d;
-        const float* qr = a.q + (size_t)t * a.q_t + (size_t)g * d;
-        const float* gr = a.decay + (size_t)t * a.decay_t + (size_t)h * d;
-        const float* vr = a.v + (size_t)t * a.v_t + (size_t)h * dv;
-        for (int i = threadIdx.x; i < row; i += blockDim.x)
-            dst[i] = i < d ? kr[i] : (i < 2 * d ? qr[i - d] : (i < 3 * d ? gr[i - 2 * d] : vr[i - 3 * d]));
+    // the padding of every row of the ring, once: keys and queries 0, decay 1, values 0
+    for (int i = threadIdx.x; i < DS_STAGES * stage_tokens * ROW; i += blockDim.x) {
+        const int e = i % ROW;
+        smem[i] = (e >= 2 * DP && e < 3 * DP) ? 1.f : 0.f;
+    }
+    __syncthreads();
+    const int ncols = min(COLS, dv - j0);
+    const int stages = (end - begin + stage_tokens - 1) / stage_tokens;
+    auto issue = [&](int s) {                            // the copying warp only
+        if (s < stages) {
+            float* dst0 = smem + (size_t)(s % DS_STAGES) * stage_tokens * ROW;
+            const int t0 = begin + s * stage_tokens;
+            const int cnt = min(stage_tokens, end - t0);
+            for (int tt = 0; tt < cnt; ++tt) {
+                const int t = t0 + tt;
+                float* dst = dst0 + (size_t)tt * ROW;
+                ds_copy_row(dst, a.k + (size_t)t * a.k_t + (size_t)g * d, d, vec & 1, lane);
+                ds_copy_row(dst + DP, a.q + (size_t)t * a.q_t + (size_t)g * d, d, vec & 1, lane);
+                ds_copy_row(dst + 2 * DP, a.decay + (size_t)t * a.decay_t + (size_t)h * d, d, vec & 2, lane);
+                ds_copy_row(dst + 3 * DP, a.v + (size_t)t * a.v_t + (size_t)h * dv + j0, ncols, vec & 4, lane);
+                if (lane == 0) ds_cp_async_4(dst + 3 * DP + COLS, a.beta + (size_t)t * a.beta_t + h);
+            }
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
     };
-    fetch(begin, buf);
-    for (int t = begin; t < end; ++t) {
-        const float* cur = buf + ((t - begin) & 1) * row;
-        __syncthreads();
-        const float beta = a.beta[(size_t)t * a.beta_t + h];
-        if (owner) {
-            float sk = 0.f, sq = 0.f, kq = 0.f;
+    if (loader) { issue(0); issue(1); }
+    for (int s = 0; s < stages; ++s) {
+        if (loader) asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        __syncthreads();                                 // stage s is here; everyone has left stage s - 1
+        if (loader) {
+            issue(s + 2);                                // into the buffer of stage s - 1
+            continue;
+        }
+        const float* base = smem + (size_t)(s % DS_STAGES) * stage_tokens * ROW;
+        const int t0 = begin + s * stage_tokens;
+        const int cnt = min(stage_tokens, end - t0);
+        for (int tt = 0; tt < cnt; ++tt) {
+            const float* cur = base + (size_t)tt * ROW;
+            float kc[NT];
+            float sk[2] = {0.f, 0.f}, sq[2] = {0.f, 0.f}, kq = 0.f;
 #pragma unroll
-            for (int i = 0; i < NT; ++i) {
-                const int c = rr + i * R;
-                if (c < d) {
-                    S[i] *= cur[2 * d + c];
-                    sk = fmaf(S[i], cur[c], sk);
-                    sq = fmaf(S[i], cur[d + c], sq);
-                    kq = fmaf(cur[c], cur[d + c], kq);
+            for (int i4 = 0; i4 < NT / V; ++i4) {
+                const int at = (i4 * R + rr) * V;
+                const DsVec<V> kk = ds_load<V>(cur + at), qq = ds_load<V>(cur + DP + at), gg = ds_load<V>(cur + 2 * DP + at);
+#pragma unroll
+                for (int e = 0; e < V; ++e) {
+                    const int i = i4 * V + e;
+                    kc[i] = kk.v[e];
+                    S[i] *= gg.v[e];
+                    sk[e & 1] = fmaf(S[i], kk.v[e], sk[e & 1]);
+                    sq[e & 1] = fmaf(S[i], qq.v[e], sq[e & 1]);
+                    kq = fmaf(kk.v[e], qq.v[e], kq);
                 }
             }
-            part[rr * ps + j] = sk;
-            part[rr * ps + dv + j] = sq;
-            if (j == 0) part[rr * ps + 2 * dv] = kq;
-        }
-        if (t + 1 < end) fetch(t + 1, buf + ((t + 1 - begin) & 1) * row);
-        __syncthreads();
-        if (owner) {
-            float sk = 0.f, sq = 0.f, kq = 0.f;
-            for (int i = 0; i < R; ++i) {
-                sk += part[i * ps + j];
-                sq += part[i * ps + dv + j];
-                kq += part[i * ps + 2 * dv];
-            }
-            const float u = beta * (cur[3 * d + j] - sk);
+            float sks = sk[0] + sk[1], sqs = sq[0] + sq[1];
 #pragma unroll
-            for (int i = 0; i < NT; ++i) {
-                const int c = rr + i * R;
-                if (c < d) S[i] = fmaf(cur[c], u, S[i]);
+            for (int m = R >> 1; m > 0; m >>= 1) {
+                sks += __shfl_xor_sync(0xffffffffu, sks, m);
+                sqs += __shfl_xor_sync(0xffffffffu, sqs, m);
+                kq += __shfl_xor_sync(0xffffffffu, kq, m);
             }
-            if (rr == 0) a.o[(size_t)t * a.o_t + (size_t)h * dv + j] = fmaf(u, kq, sq);
+            const float u = cur[3 * DP + COLS] * (cur[3 * DP + col] - sks);
+#pragma unroll
+            for (int i = 0; i < NT; ++i) S[i] = fmaf(kc[i], u, S[i]);
+            if (rr == 0 && valid) a.o[(size_t)(t0 + tt) * a.o_t + (size_t)h * dv + j] = fmaf(u, kq, sqs);
         }
     }
-    if (owner) {
+    if (loader) asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    if (valid) {
 #pragma unroll
         for (int i = 0; i < NT; ++i) {
-            const int c = rr + i * R;
+            const int c = ((i / V) * R + rr) * V + i % V;
             if (c < d) wr[(size_t)c * dv + j] = S[i];
         }
     }
@@ -155,32 +211,42 @@ LLMP_API int llmp_delta_scan(const float* q, long q_t, const float* k, long k_t,
     if (R <= 0) return 0;
     LLMP_REQUIRE(H > 0 && G > 0 && H % G == 0 && d > 0 && dv > 0 && dv <= 1024 && H <= 65535,
                  "delta_scan: bad sizes heads=%d qk_heads=%d dim=%d vdim=%d", H, G, d, dv);
+    LLMP_REQUIRE((dv + 3) / 4 <= 65535, "delta_scan: too many value columns %d", dv);
     DeltaArgs a;
     a.q = q; a.q_t = q_t; a.k = k; a.k_t = k_t; a.v = v; a.v_t = v_t; a.decay = decay; a.decay_t = decay_t;
     a.beta = beta; a.beta_t = beta_t; a.state = state; a.state_slot = state_slot; a.state_half = state_half;
     a.q_start = q_start; a.slots = slots; a.positions = positions; a.o = o; a.o_t = o_t; a.H = H; a.G = G; a.d = d; a.dv = dv;
-    // threads in whole columns; the rows a thread holds are bounded by the registers a block of that size may use
-    int threads = 0;
-    const int choices[4][2] = {{256, 32}, {512, 32}, {256, 64}, {1024, 8}};
-    for (int i = 0; i < 4 && !threads; ++i) {
-        const int groups = choices[i][0] / dv;
-        if (groups > 0 && (d + groups - 1) / groups <= choices[i][1]) threads = choices[i][0];
-    }
-    LLMP_REQUIRE(threads > 0, "delta_scan: a state of %d x %d does not fit the registers of a block", d, dv);
-    const int rows = threads / dv;
+    // lanes that share a column: the fewest (a power of two up to 32) that leave a lane at most 16 rows (32 past 512 rows)
+    int rows = 1;
+    while (rows < 32 && (d + rows - 1) / rows > 16) rows *= 2;
     const int per = (d + rows - 1) / rows;
-    const size_t smem = ((size_t)2 * (3 * d + dv) + (size_t)rows * (2 * dv + 1)) * sizeof(float);
+    LLMP_REQUIRE(per <= 32, "delta_scan: a state of %d rows does not fit the registers of a warp", d);
+    int nt = 1;
+    while (nt < per) nt *= 2;
+    if (rows > 1) nt = nt < 16 ? 16 : nt;
+    const int cols = DS_THREADS / rows;
+    const size_t row_bytes = (size_t)(3 * nt * rows + cols + 4) * sizeof(float);
+    int stage_tokens = 8;
+    while (stage_tokens > 1 && DS_STAGES * stage_tokens * row_bytes > 96 * 1024) stage_tokens /= 2;
+    const size_t smem = DS_STAGES * stage_tokens * row_bytes;
     LLMP_REQUIRE(smem <= 200 * 1024, "delta_scan: heads of %d x %d do not fit shared memory", d, dv);
-    dim3 grid(R, H);
-#define LLMP_DELTA(NT)                                                   \
-    do {                                                                 \
-        LLMP_ALLOW_SMEM(delta_scan_kernel<NT>, smem);                    \
-        delta_scan_kernel<NT><<<grid, threads, smem, stream>>>(a);       \
-    } while (0)
-    if (per <= 8) LLMP_DELTA(8);
-    else if (per <= 16) LLMP_DELTA(16);
-    else if (per <= 32) LLMP_DELTA(32);
-    else LLMP_DELTA(64);
+    auto aligned = [](const void* p, long stride) { return ((uintptr_t)p & 15) == 0 && stride % 4 == 0; };
+    int vec = 0;
+    if (d % 4 == 0 && aligned(q, q_t) && aligned(k, k_t)) vec |= 1;
+    if (d % 4 == 0 && aligned(decay, decay_t)) vec |= 2;
+    if (dv % 4 == 0 && (nt * rows) % 4 == 0 && aligned(v, v_t)) vec |= 4;     // the columns' place in a ring row is aligned too
+    dim3 grid(R, H, (dv + cols - 1) / cols);
+#define LLMP_DELTA(NT, RW)                                                                          \
+    if (nt == NT && rows == RW) {                                                                   \
+        LLMP_ALLOW_SMEM((delta_scan_kernel<NT, RW>), smem);                                         \
+        delta_scan_kernel<NT, RW><<<grid, DS_THREADS + 32, smem, stream>>>(a, stage_tokens, vec);   \
+    } else
+    LLMP_DELTA(1, 1) LLMP_DELTA(2, 1) LLMP_DELTA(4, 1) LLMP_DELTA(8, 1) LLMP_DELTA(16, 1) LLMP_DELTA(16, 2) LLMP_DELTA(16, 4)
+    LLMP_DELTA(16, 8) LLMP_DELTA(16, 16) LLMP_DELTA(16, 32) LLMP_DELTA(32, 32)
+    {
+        llmp_set_error("delta_scan: no instance for %d rows a lane on %d lanes", nt, rows);
+        return 1;
+    }
 #undef LLMP_DELTA
     return llmp_check_launch("delta_scan");
 }

@@ -97,6 +97,7 @@ __global__ void __launch_bounds__(SM_MAX_HEADS * 32, 1) sigmoid_attention_mma_ke
     if (a.segments > 1) {
         lo = seg * a.segment_keys;
         hi = min(hi, lo + a.segment_keys - 1);
+        if (lo > hi) return;                                        // nothing of this range is visible: its sums are never read
     }
     const int* table = a.tables + (size_t)r * a.width;
 

@@ -1304,6 +1304,7 @@ def sig_qkv_post(qkv: torch.Tensor, bias: Optional[torch.Tensor], cos: Optional[
 SIGMOID_MAX_HEADS = 32             # query heads whose weights one block of the sigmoid attention kernel mixes
 SIGMOID_SEGMENT_KEYS = 1024       # keys of a segment when a token's keys are shared among blocks (a multiple of the key tile)
 SIGMOID_MMA_SEGMENT_KEYS = 128    # the same for the tensor-core kernel, whose blocks walk a tile of keys for up to 16 tokens at once
+SIGMOID_MMA_LONG_SEGMENT_KEYS = 1024   # ranges of long prompts whose tiles are too few for two rounds of blocks
 SIGMOID_MMA_ROWS = 16             # new tokens of a request in a tile of the tensor-core kernel
 
 
@@ -1346,10 +1347,11 @@ def sigmoid_attention_mma_supports(dtype: torch.dtype, heads: int, kv_heads: int
 def sigmoid_attention_mma(q: torch.Tensor, pages: torch.Tensor, tables: torch.Tensor, q_start: torch.Tensor, ctx_len: torch.Tensor,
                           positions: torch.Tensor, tile_req: torch.Tensor, tile_tok0: torch.Tensor, talk: torch.Tensor,
                           head_bias: torch.Tensor, out: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int, scale: float,
-                          softcap: float, segments: int = 1) -> torch.Tensor:
+                          softcap: float, segments: int = 1, segment_keys: int = 0) -> torch.Tensor:
     """``sigmoid_attention`` on the tensor cores for bfloat16 (csrc/sigmoid_attention_mma.cu). ``tile_req``/``tile_tok0``: the
     work list (request and first new token of every tile of ``SIGMOID_MMA_ROWS`` tokens), in the order of the keys a tile
-    sees. ``segments`` > 1: fixed ranges of ``SIGMOID_MMA_SEGMENT_KEYS`` keys go to blocks of their own."""
+    sees. ``segments`` > 1: fixed ranges of ``segment_keys`` keys (a multiple of 32; ``SIGMOID_MMA_SEGMENT_KEYS`` when 0) go to
+    blocks of their own."""
     N = q.shape[0]
     _need(q.dtype == out.dtype == pages.dtype == torch.bfloat16 and q.shape == (N, heads * dim) and q.stride(1) == 1 and
           out.shape == (N, heads * vdim) and out.stride(1) == 1, "sigmoid_attention_mma takes bfloat16 queries, pages and output of matching shapes")
@@ -1366,7 +1368,7 @@ def sigmoid_attention_mma(q: torch.Tensor, pages: torch.Tensor, tables: torch.Te
         partial = torch.empty((N, segments, heads * vdim), dtype=torch.float32, device=q.device)
     _call("llmp_sigmoid_attention_mma", _ptr(q), q.stride(0), _ptr(pages), _ptr(tables), tables.shape[1], _ptr(q_start), _ptr(ctx_len),
           _ptr(positions), _ptr(tile_req), _ptr(tile_tok0), tile_req.numel(), _ptr(talk), _ptr(head_bias), _ptr(out), out.stride(0),
-          _ptr(partial), int(segments), SIGMOID_MMA_SEGMENT_KEYS, N, heads, kv_heads, dim, vdim, pages.shape[2], float(scale),
+          _ptr(partial), int(segments), int(segment_keys) or SIGMOID_MMA_SEGMENT_KEYS, N, heads, kv_heads, dim, vdim, pages.shape[2], float(scale),
           float(softcap or 0.0), _stream())
     return out
 

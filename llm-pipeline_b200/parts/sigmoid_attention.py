@@ -40,6 +40,7 @@ class SigmoidAttention(Mixer):
     # Blocks per SM below which a step's tokens are too few to fill the GPU and the keys are cut into segments.
     SEGMENTS_BELOW_BLOCKS_PER_SM = 2.0
     MMA_SEGMENTS_BELOW_BLOCKS_PER_SM = 0.5      # the same for the tensor-core kernel, a block of which fills an SM
+    MMA_LONG_SEGMENTS_BELOW_BLOCKS_PER_SM = 2.0 # below this, long prompts are cut into long key ranges
     SEGMENTS_MAX_BYTES = 256 << 20              # the float32 partial sums of all segments never take more than this
 
     def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float,
@@ -74,22 +75,37 @@ class SigmoidAttention(Mixer):
         return ("sigmoid_attention", self.num_heads)
 
     def graph_key(self, shape) -> int:
-        """The number of key segments a step of single tokens takes: a captured step holds the grid it was captured with."""
-        return self._segments(shape.num_requests, shape.longest)
+        """The key ranges a step of single tokens takes (their number and size): a captured step holds the grid it was
+        captured with."""
+        segments, keys = self._segments(shape.num_requests, shape.longest)
+        return segments | keys << 20
 
-    def _segments(self, tokens: int, longest: int) -> int:
+    def _segments(self, tokens: int, longest: int):
+        """(number of key ranges, keys of a range) for a step of ``tokens`` new tokens whose longest context is ``longest``."""
         if self._mma is None:
             self._mma = kernels.sigmoid_attention_mma_supports(self.compute_dtype, self.num_heads, self.num_kv_heads, self.dim, self.vdim)
-        blocks, keys, below = tokens, kernels.SIGMOID_SEGMENT_KEYS, self.SEGMENTS_BELOW_BLOCKS_PER_SM
-        if self._mma:
-            # a lower bound of the tiles (a request's last tile may be short); single tokens give exactly one tile each
-            blocks, keys, below = -(-tokens // kernels.SIGMOID_MMA_ROWS), kernels.SIGMOID_MMA_SEGMENT_KEYS, self.MMA_SEGMENTS_BELOW_BLOCKS_PER_SM
-        if blocks >= below * kernels.sm_count() or longest <= keys:
-            return 1
+        sms = kernels.sm_count()
+        if not self._mma:
+            keys = kernels.SIGMOID_SEGMENT_KEYS
+            if tokens >= self.SEGMENTS_BELOW_BLOCKS_PER_SM * sms or longest <= keys:
+                return 1, keys
+        else:
+            # tiles of the tensor-core kernel, a block of which fills an SM (a lower bound: a request's last tile may be
+            # short). Very few: short ranges, so that every SM gets a block. Fewer than two rounds of blocks over long
+            # prompts: long ranges, so that the tiles that see most keys do not take twice the average.
+            blocks = -(-tokens // kernels.SIGMOID_MMA_ROWS)
+            if blocks < self.MMA_SEGMENTS_BELOW_BLOCKS_PER_SM * sms:
+                keys = kernels.SIGMOID_MMA_SEGMENT_KEYS
+            elif blocks < self.MMA_LONG_SEGMENTS_BELOW_BLOCKS_PER_SM * sms:
+                keys = kernels.SIGMOID_MMA_LONG_SEGMENT_KEYS
+            else:
+                return 1, kernels.SIGMOID_MMA_SEGMENT_KEYS
+            if longest <= keys:
+                return 1, keys
         segments = -(-longest // keys)
         if tokens * segments * self.num_heads * self.vdim * 4 > self.SEGMENTS_MAX_BYTES:
-            return 1
-        return segments
+            return 1, keys
+        return segments, keys
 
     def _tiles(self, ctx):
         key = ("sigmoid_attention_tiles", kernels.SIGMOID_MMA_ROWS)
@@ -148,12 +164,12 @@ class SigmoidAttention(Mixer):
         kernels.sig_qkv_post(qkv, self.b_qkv, cos, sin, self.rotary_dim, q, ctx.slot_mapping[cache.group] if cache.writes else None,
                              cache.pages if cache.writes else None, self.num_heads, self.num_kv_heads, self.dim, self.vdim)
         out = torch.empty((N, self.num_heads * self.vdim), dtype=x.dtype, device=x.device)
-        segments = self._segments(N, ctx.decode_ctx_bound or ctx.max_ctx_len)
+        segments, segment_keys = self._segments(N, ctx.decode_ctx_bound or ctx.max_ctx_len)
         sizes = (self.num_heads, self.num_kv_heads, self.dim, self.vdim, self.scale, self.softcap, segments)
         if self._mma and q.dtype == torch.bfloat16:
             tile_req, tile_tok0 = self._tiles(ctx)
             kernels.sigmoid_attention_mma(q, cache.pages, ctx.block_tables[cache.group], ctx.q_start, ctx.ctx_len, ctx.positions,
-                                          tile_req, tile_tok0, self.talk, self.pb, out, *sizes)
+                                          tile_req, tile_tok0, self.talk, self.pb, out, *sizes, segment_keys=segment_keys)
         else:
             kernels.sigmoid_attention(q, cache.pages, ctx.block_tables[cache.group], ctx.token_request, ctx.positions, self.talk,
                                       self.pb, out, *sizes)

@@ -53,7 +53,7 @@ def test_activation_gated_norms_and_weighted_sum_alone(dtype):
         assert (got.cpu().double() - (1.7 * a.double() - 0.4 * b.double())).abs().max() < 1e-6
     # rows normed in equal parts: gate first (y silu(z), then the norm, a weight per column), and gate last (the norm,
     # a weight per column of the part, then sigmoid(z))
-    for rows, parts, size in ((4, 1, 48), (6, 3, 20), (2, 5, 7)):
+    for rows, parts, size in ((4, 1, 48), (6, 3, 20), (2, 5, 7), (3, 2, 520), (2, 1, 2100)):     # the last two: a block per part
         y, g = torch.randn(rows, parts * size) * 2, torch.randn(rows, parts * size)
         w_row, w_part = 1 + 0.3 * torch.randn(parts * size), 1 + 0.3 * torch.randn(size)
         out = torch.empty(rows, parts * size, device=dev, dtype=dtype)
@@ -109,7 +109,8 @@ def _scan_in_portions(launch, n, cuts, state_entries, offset):
     return state
 
 
-@pytest.mark.parametrize("sizes", [(4, 2, 24, 16), (3, 3, 7, 12), (2, 1, 64, 32), (5, 1, 16, 128)], ids=str)
+@pytest.mark.parametrize("sizes", [(4, 2, 24, 16), (3, 3, 7, 12), (2, 1, 64, 32), (5, 1, 16, 128), (2, 2, 200, 9), (1, 1, 530, 3),
+                                   (2, 1, 128, 64), (3, 1, 1, 5)], ids=str)
 def test_state_space_recurrence_alone(sizes):
     """The scan kernel against the recurrence written out, whole and in portions of 1, 2 and more tokens: heads that share a
     group of state channels, state channels more and fewer than value channels, decays from near 0 to near 1."""
@@ -142,7 +143,8 @@ def test_state_space_recurrence_alone(sizes):
         assert (y.cpu().double() - want.view(n, -1)).abs().max() < 2e-4 * max(1.0, float(want.abs().max())), cuts
 
 
-@pytest.mark.parametrize("sizes", [(4, 2, 16, 24), (3, 3, 12, 5), (2, 1, 64, 32), (1, 1, 32, 128), (6, 1, 128, 16)], ids=str)
+@pytest.mark.parametrize("sizes", [(4, 2, 16, 24), (3, 3, 12, 5), (2, 1, 64, 32), (1, 1, 32, 128), (6, 1, 128, 16), (2, 2, 200, 9),
+                                   (1, 1, 530, 3), (2, 1, 96, 40), (3, 1, 1, 5)], ids=str)
 def test_gated_delta_rule_alone(sizes):
     """Unit vectors, step sizes and decays (the preparing kernel) and the scan against the rule written out, whole and in
     portions: the read-out sees the token's own write, heads share query/key heads, keys wider and narrower than values."""
