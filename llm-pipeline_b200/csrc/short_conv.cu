@@ -10,8 +10,9 @@
 // Two forms with the same arithmetic (the products are summed from the oldest input to the current one, then the bias):
 //   serial:   a thread per (request, channel) walks the request's tokens with the last inputs in registers and writes the
 //             state at the end; for steps whose requests bring few tokens (decode steps above all).
-//   parallel: a thread per (token, channel) takes earlier inputs from the step's rows or, before the portion's first
-//             token, from the state; a second kernel then moves the state on.
+//   parallel: a thread per (tile of 16 tokens of the step, channel) walks the tile the same way, taking the inputs before
+//             the tile from the step's rows or, before the portion's first token, from the state; a second kernel then
+//             moves the state on.
 // Inputs and outputs are float32 (what follows is a recurrence in 32-bit); taps and bias have the type they were stored in.
 #include "common.cuh"
 
@@ -71,26 +72,57 @@ __global__ void short_conv_serial_kernel(const ConvArgs a) {
         if (j < K - 1) wr[(size_t)j * a.C + c] = w[j];
 }
 
-__global__ void short_conv_parallel_kernel(const ConvArgs a) {
-    const int t = blockIdx.x;
+constexpr int CONV_TILE_TOKENS = 16;
+
+// A block takes CONV_TILE_TOKENS consecutive tokens of the step and 128 channels; a thread walks its channel through
+// the tile with the last K - 1 inputs in registers, and fills them anew where the tile begins or a new request does
+// (from the step's rows, or from the slot's copy for places before the portion).
+__global__ void short_conv_parallel_kernel(const ConvArgs a, const int N) {
+    const int t0 = blockIdx.x * CONV_TILE_TOKENS;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= a.C) return;
-    const int r = a.token_request[t];
-    const int begin = a.q_start[r];
-    const int p0 = a.positions[begin];
-    const float* rd = a.state + (size_t)a.slots[r] * a.state_slot + ((p0 + 1) & 1) * a.state_half;
     const int K = a.K;
-    float acc = 0.f;
-    for (int j = 0; j < K; ++j) {
-        const int at = t - (K - 1) + j;
-        const float v = at >= begin ? a.x[(size_t)at * a.x_t + c] : rd[(size_t)(K - 1 + at - begin) * a.C + c];
-        acc = fmaf(v, load_as_float(a.taps, a.taps_bf16, (size_t)c * K + j), acc);
+    float w[CONV_MAX_TAPS], tap[CONV_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+        tap[j] = j < K ? load_as_float(a.taps, a.taps_bf16, (size_t)c * K + j) : 0.f;
+        w[j] = 0.f;
     }
+    float last = 0.f;
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; ++j)
+        if (j == K - 1) last = tap[j];
     const float b = a.bias ? load_as_float(a.bias, a.bias_bf16, c) : 0.f;
-    a.out[(size_t)t * a.out_t + c] = conv_act(acc + b, a.act);
+    const int t1 = min(t0 + CONV_TILE_TOKENS, N);
+    int r_prev = -1;
+    for (int t = t0; t < t1; ++t) {
+        const int r = a.token_request[t];
+        if (r != r_prev) {
+            r_prev = r;
+            const int begin = a.q_start[r];
+            const int p0 = a.positions[begin];
+            const float* rd = a.state + (size_t)a.slots[r] * a.state_slot + ((p0 + 1) & 1) * a.state_half;
+#pragma unroll
+            for (int j = 0; j < CONV_MAX_TAPS - 1; ++j) {
+                if (j < K - 1) {
+                    const int at = t - (K - 1) + j;
+                    w[j] = at >= begin ? a.x[(size_t)at * a.x_t + c] : rd[(size_t)(K - 1 + at - begin) * a.C + c];
+                }
+            }
+        }
+        const float xin = a.x[(size_t)t * a.x_t + c];
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
+            if (j < K - 1) acc = fmaf(w[j], tap[j], acc);
+        acc = fmaf(xin, last, acc);
+        a.out[(size_t)t * a.out_t + c] = conv_act(acc + b, a.act);
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
+            if (j < K - 1) w[j] = (j + 1 < K - 1) ? w[j + 1] : xin;
+    }
 }
 
-// After the parallel form: the last K - 1 inputs of (old state, then the portion) become the state.
 __global__ void short_conv_state_kernel(const ConvArgs a) {
     const int r = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -140,7 +172,7 @@ LLMP_API int llmp_short_conv(const float* x, long x_t, const void* taps, int tap
         short_conv_serial_kernel<<<dim3(R, col_blocks), threads, 0, stream>>>(a);
         return llmp_check_launch("short_conv");
     }
-    short_conv_parallel_kernel<<<dim3(N, col_blocks), threads, 0, stream>>>(a);
+    short_conv_parallel_kernel<<<dim3((N + CONV_TILE_TOKENS - 1) / CONV_TILE_TOKENS, col_blocks), threads, 0, stream>>>(a, N);
     if (K > 1) short_conv_state_kernel<<<dim3(R, col_blocks), threads, 0, stream>>>(a);
     return llmp_check_launch("short_conv (parallel)");
 }
