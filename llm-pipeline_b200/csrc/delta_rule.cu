@@ -55,6 +55,7 @@ struct DeltaArgs {
 };
 
 constexpr int DS_THREADS = 128;   // threads of a block that hold the state; one more warp copies the inputs
+constexpr int DS_COPY_WARPS = 4;   // warps that copy the inputs, one per scheduler: a single warp's chain of addresses and copies was the bound
 constexpr int DS_STAGES = 3;      // stages of the input ring
 
 __device__ __forceinline__ void ds_cp_async_4(float* smem_dst, const float* gmem_src) {
@@ -84,11 +85,11 @@ template <int V> __device__ __forceinline__ DsVec<V> ds_load(const float* p) {
 // between blocks. Within a warp, R consecutive lanes share a column: lane (column, r) holds NT state rows of its column
 // in registers, in runs of V = min(NT, 4) rows (run i of lane r: rows (i R + r) V ..), so that a lane reads its keys,
 // queries and decays as 16-byte words and the lanes of a column read consecutive words; rows past d are zeros that
-// stay zeros. The sums over rows are rounds of shuffles. A fifth warp copies the tokens' inputs through a ring of
+// stay zeros. The sums over rows are rounds of shuffles. Four more warps copy the tokens' inputs through a ring of
 // DS_STAGES stages of `stage_tokens` tokens (cp.async, 16 bytes where the rows allow it), so a block synchronises once
 // per stage, not per token, and the warps that hold the state do no address arithmetic for the copies.
 template <int NT, int R>
-__global__ void __launch_bounds__(DS_THREADS + 32) delta_scan_kernel(const DeltaArgs a, const int stage_tokens, const int vec) {
+__global__ void __launch_bounds__(DS_THREADS + 32 * DS_COPY_WARPS) delta_scan_kernel(const DeltaArgs a, const int stage_tokens, const int vec) {
     extern __shared__ __align__(16) float smem[];
     constexpr int V = NT < 4 ? NT : 4;
     constexpr int DP = NT * R;                           // rows with padding
@@ -99,6 +100,7 @@ __global__ void __launch_bounds__(DS_THREADS + 32) delta_scan_kernel(const Delta
     if (end <= begin) return;
     const int d = a.d, dv = a.dv;
     const bool loader = threadIdx.x >= DS_THREADS;
+    const int copy_warp = ((int)threadIdx.x - DS_THREADS) >> 5;      // which of the copying warps (negative for the others)
     const int lane = threadIdx.x & 31;
     const int rr = threadIdx.x % R, col = (threadIdx.x / R) % COLS;
     const int j0 = blockIdx.z * COLS, j = j0 + col;
@@ -127,7 +129,7 @@ __global__ void __launch_bounds__(DS_THREADS + 32) delta_scan_kernel(const Delta
             float* dst0 = smem + (size_t)(s % DS_STAGES) * stage_tokens * ROW;
             const int t0 = begin + s * stage_tokens;
             const int cnt = min(stage_tokens, end - t0);
-            for (int tt = 0; tt < cnt; ++tt) {
+            for (int tt = copy_warp; tt < cnt; tt += DS_COPY_WARPS) {
                 const int t = t0 + tt;
                 float* dst = dst0 + (size_t)tt * ROW;
                 ds_copy_row(dst, a.k + (size_t)t * a.k_t + (size_t)g * d, d, vec & 1, lane);
@@ -239,7 +241,7 @@ LLMP_API int llmp_delta_scan(const float* q, long q_t, const float* k, long k_t,
 #define LLMP_DELTA(NT, RW)                                                                          \
     if (nt == NT && rows == RW) {                                                                   \
         LLMP_ALLOW_SMEM((delta_scan_kernel<NT, RW>), smem);                                         \
-        delta_scan_kernel<NT, RW><<<grid, DS_THREADS + 32, smem, stream>>>(a, stage_tokens, vec);   \
+        delta_scan_kernel<NT, RW><<<grid, DS_THREADS + 32 * DS_COPY_WARPS, smem, stream>>>(a, stage_tokens, vec);   \
     } else
     LLMP_DELTA(1, 1) LLMP_DELTA(2, 1) LLMP_DELTA(4, 1) LLMP_DELTA(8, 1) LLMP_DELTA(16, 1) LLMP_DELTA(16, 2) LLMP_DELTA(16, 4)
     LLMP_DELTA(16, 8) LLMP_DELTA(16, 16) LLMP_DELTA(16, 32) LLMP_DELTA(32, 32)

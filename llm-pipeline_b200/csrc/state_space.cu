@@ -27,6 +27,7 @@ struct ScanArgs {
 };
 
 constexpr int SS_THREADS = 128;   // threads of a block that hold the state; one more warp copies the inputs
+constexpr int SS_COPY_WARPS = 4;   // warps that copy the inputs, one per scheduler: a single warp's chain of addresses and copies was the bound
 constexpr int SS_STAGES = 3;      // stages of the input ring
 
 __device__ __forceinline__ void ss_cp_async_4(float* smem_dst, const float* gmem_src) {
@@ -54,11 +55,12 @@ template <int V> __device__ __forceinline__ SsVec<V> ss_load(const float* p) {
 // A block owns (request, head, a range of the head's columns); the columns of the state never meet. Within a warp, R
 // consecutive lanes share a column: lane (column, r) holds NT state rows of its column in registers, in runs of
 // V = min(NT, 4) rows (run i of lane r: rows (i R + r) V ..), so that B and C are read as 16-byte words; rows past N
-// see B = C = 0 and stay zero. The sum over rows is a round of shuffles. A fifth warp copies the tokens' inputs
-// through a ring of SS_STAGES stages of `stage_tokens` tokens (cp.async, 16 bytes where the rows allow it) and turns
-// each token's raw step size into (dt, decay) before the stage's barrier: one barrier per stage, not per token.
+// see B = C = 0 and stay zero. The sum over rows is a round of shuffles. Four more warps copy the tokens' inputs
+// through a ring of SS_STAGES stages of `stage_tokens` tokens (cp.async, 16 bytes where the rows allow it), a token
+// each in turn, and the first of them turns each token's raw step size into (dt, decay) before the stage's barrier:
+// one barrier per stage, not per token.
 template <int NT, int R>
-__global__ void __launch_bounds__(SS_THREADS + 32) ssd_scan_kernel(const ScanArgs a, const int stage_tokens, const int vec) {
+__global__ void __launch_bounds__(SS_THREADS + 32 * SS_COPY_WARPS) ssd_scan_kernel(const ScanArgs a, const int stage_tokens, const int vec) {
     extern __shared__ __align__(16) float smem[];
     constexpr int V = NT < 4 ? NT : 4;
     constexpr int NP = NT * R;                          // rows with padding
@@ -69,6 +71,7 @@ __global__ void __launch_bounds__(SS_THREADS + 32) ssd_scan_kernel(const ScanArg
     if (end <= begin) return;
     const int N = a.N, P = a.P;
     const bool loader = threadIdx.x >= SS_THREADS;
+    const int copy_warp = ((int)threadIdx.x - SS_THREADS) >> 5;      // which of the copying warps (negative for the others)
     const int lane = threadIdx.x & 31;
     const int rr = threadIdx.x % R, col = (threadIdx.x / R) % COLS;
     const int j0 = blockIdx.z * COLS, p = j0 + col;
@@ -95,7 +98,7 @@ __global__ void __launch_bounds__(SS_THREADS + 32) ssd_scan_kernel(const ScanArg
             float* dst0 = smem + (size_t)(s % SS_STAGES) * stage_tokens * ROW;
             const int t0 = begin + s * stage_tokens;
             const int cnt = min(stage_tokens, end - t0);
-            for (int tt = 0; tt < cnt; ++tt) {
+            for (int tt = copy_warp; tt < cnt; tt += SS_COPY_WARPS) {
                 const float* src = a.xbc + (size_t)(t0 + tt) * a.xbc_t;
                 float* dst = dst0 + (size_t)tt * ROW;
                 ss_copy_row(dst, src + b_at, N, vec & 1, lane);
@@ -111,7 +114,7 @@ __global__ void __launch_bounds__(SS_THREADS + 32) ssd_scan_kernel(const ScanArg
         const int t0 = begin + s * stage_tokens;
         const int cnt = min(stage_tokens, end - t0);
         if (loader) {
-            for (int tt = lane; tt < cnt; tt += 32) {   // step sizes and decays of the stage's tokens
+            for (int tt = lane; tt < cnt && copy_warp == 0; tt += 32) {   // step sizes and decays of the stage's tokens
                 const float dt = softplus_f(a.dt[(size_t)(t0 + tt) * a.dt_t + h] + bias);
                 base[(size_t)tt * ROW + 2 * NP + COLS] = dt;
                 base[(size_t)tt * ROW + 2 * NP + COLS + 1] = expf(neg_a * dt);
@@ -228,7 +231,7 @@ LLMP_API int llmp_ssd_scan(const float* xbc, long xbc_t, const float* dt, long d
 #define LLMP_SCAN(NT, RW)                                                                         \
     if (nt == NT && rows == RW) {                                                                 \
         LLMP_ALLOW_SMEM((ssd_scan_kernel<NT, RW>), smem);                                         \
-        ssd_scan_kernel<NT, RW><<<grid, SS_THREADS + 32, smem, stream>>>(a, stage_tokens, vec);   \
+        ssd_scan_kernel<NT, RW><<<grid, SS_THREADS + 32 * SS_COPY_WARPS, smem, stream>>>(a, stage_tokens, vec);   \
     } else
     LLMP_SCAN(1, 1) LLMP_SCAN(2, 1) LLMP_SCAN(4, 1) LLMP_SCAN(8, 1) LLMP_SCAN(16, 1) LLMP_SCAN(16, 2) LLMP_SCAN(16, 4)
     LLMP_SCAN(16, 8) LLMP_SCAN(16, 16) LLMP_SCAN(16, 32) LLMP_SCAN(32, 32)
