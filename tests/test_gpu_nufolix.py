@@ -388,31 +388,41 @@ def test_far_keys_page_borders_and_first_tokens_under_sparse_weights(tmp_path, n
     N.assert_matches(H.replay(runner, H.cut_mixed(requests, (page, 2, page + 1), max_live=3, decode_tail=page + 3)), want, dtype, "sparse: mixed", share)
 
 
-def test_few_rows_over_long_contexts_take_key_segments(tmp_path):
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_few_rows_over_long_contexts_take_key_segments(tmp_path, dtype):
     """Contexts of several key segments under sparse weights: decoding steps and short portions share a token's keys among
-    blocks whose sums a second kernel adds; positions around the segment borders, and long portions that take one block."""
+    blocks whose sums a second kernel adds; positions around the segment borders, and long portions that take one block.
+    In float32 the general kernel runs, in bfloat16 the tensor-core kernel with its shorter key ranges."""
     from llm_pipeline_b200.ops import kernels
-    dtype = torch.float32
     cfg, W, folder = case(tmp_path, "attention_first", 8, sharp=5.0, head_bias=-9.0)
     seg = kernels.SIGMOID_SEGMENT_KEYS
     requests = requests_for(cfg, [seg + 40, 2 * seg + 2, 70], 700)
     want = N.oracle(cfg, W, requests)
     runner = H.make_runner(folder, dtype, page_size=16, num_pages=3 * (seg // 16) + 16, max_request_tokens=2 * seg + 16, max_requests=3)
-    used = []
-    launch = kernels.sigmoid_attention
+    used = {"general": [], "tensor cores": []}
+    general, tensor = kernels.sigmoid_attention, kernels.sigmoid_attention_mma
 
-    def counting(*args, **kwargs):
-        used.append(args[-1] if len(args) > 14 else kwargs.get("segments", 1))
-        return launch(*args, **kwargs)
+    def counting_general(*args, **kwargs):
+        used["general"].append(args[-1] if len(args) > 14 else kwargs.get("segments", 1))
+        return general(*args, **kwargs)
 
-    kernels.sigmoid_attention = counting
+    def counting_tensor(*args, **kwargs):
+        used["tensor cores"].append((args[-1] if len(args) > 17 else kwargs.get("segments", 1), kwargs.get("segment_keys", 0)))
+        return tensor(*args, **kwargs)
+
+    kernels.sigmoid_attention, kernels.sigmoid_attention_mma = counting_general, counting_tensor
     try:
         N.assert_matches(H.replay(runner, H.cut_tail_one_by_one(requests, tail=50)), want, dtype, "segments: decoding")
         N.assert_matches(H.replay(runner, H.cut_portions(requests, (seg - 3, 2, 5, seg + 7, 3))), want, dtype, "segments: portions")
         N.assert_matches(H.replay(runner, H.cut_mixed(requests, (seg, 2, 9), max_live=3, decode_tail=12)), want, dtype, "segments: mixed")
     finally:
-        kernels.sigmoid_attention = launch
-    assert any(n > 1 for n in used) and any(n == 1 for n in used), "both forms of the kernel should have run"
+        kernels.sigmoid_attention, kernels.sigmoid_attention_mma = general, tensor
+    if dtype == torch.float32:
+        assert not used["tensor cores"] and any(n > 1 for n in used["general"]) and any(n == 1 for n in used["general"]), \
+            "both forms of the general kernel should have run"
+    else:
+        assert not used["general"] and any(n > 1 for n, _ in used["tensor cores"]), "the tensor-core kernel should have run with key ranges"
+        assert all(keys in (kernels.SIGMOID_MMA_SEGMENT_KEYS, kernels.SIGMOID_MMA_LONG_SEGMENT_KEYS) for _, keys in used["tensor cores"])
 
 
 def test_recurrent_states_carry_what_was_written_hundreds_of_tokens_back(tmp_path):
