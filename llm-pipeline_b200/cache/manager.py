@@ -11,7 +11,7 @@ the scheduler decides.
 Layers with the same need form a *group* with pages of its own: one page id addresses the same
 page in every cache of the group (a tensor ``[num_pages, *spec.page_shape(page_size)]`` per cache:
 ``[num_pages, 2, kv_heads, page_size, head_dim]`` for keys and values). A group whose layers see only a window of keys gives pages back as soon as every token
-in them has left the window; its block table then holds -1 there. Beside the pages, every live
+in them has left the window (but for the pages of the first tokens where the spec keeps those visible); its block table then holds -1 there. Beside the pages, every live
 request owns a *slot*: an index into per-cache state tensors of fixed size per request, zeroed
 when the slot is handed out.
 """
@@ -249,10 +249,11 @@ class CacheManager:
                 continue
             table = group.tables[req_id]
             keep_from = self._first_needed_page(group, new_length)
-            gone = [p for p in table[:keep_from] if p >= 0]
+            kept = -(-int(group.spec.keep_first or 0) // self.page_size)      # pages of the first tokens, which stay visible
+            gone = [p for p in table[kept:keep_from] if p >= 0]
             if gone:
                 group.pool.free(gone)
-                for i in range(min(keep_from, len(table))):
+                for i in range(kept, min(keep_from, len(table))):
                     table[i] = -1
 
     def free(self, req_id: Hashable) -> None:

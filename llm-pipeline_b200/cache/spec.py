@@ -3,7 +3,8 @@
 ``PagesSpec``: something per token, kept in pages. The spec says what one page looks like
 (``page_shape(page_size)``: the tensor of a cache is ``[num_pages, *page_shape]``), optionally its
 element type (default: the cache's), and ``window`` (None = every earlier token): pages whose
-tokens have all left the window may be given back while the request lives. Caches whose specs have
+tokens have all left the window may be given back while the request lives; with ``keep_first`` = n the
+first n tokens stay visible whatever the window, and their pages stay. Caches whose specs have
 the same ``group_key()`` share page ids and block tables. The manager, the memory budget and the
 benchmark read sizes from the spec alone (``elements_per_token``, ``bytes_per_token``).
 
@@ -29,6 +30,7 @@ class PagesSpec:
     """Base of the paged specs; a subclass is a frozen dataclass with a ``window`` field."""
 
     window: Optional[int] = None
+    keep_first: int = 0                          # tokens at a request's start that a window never leaves behind
     dtype: Optional[torch.dtype] = None          # None: the element type the cache was made with
 
     def page_shape(self, page_size: int) -> Tuple[int, ...]:
@@ -36,7 +38,7 @@ class PagesSpec:
 
     def group_key(self):
         """Caches with equal keys form one group: one pool of page ids, one block table per request."""
-        return (type(self).__name__, self.page_shape(1), self.dtype, self.window)
+        return (type(self).__name__, self.page_shape(1), self.dtype, self.window, self.keep_first if self.window is not None else 0)
 
     def elements_per_token(self) -> int:
         count = 1
@@ -66,6 +68,7 @@ class HeadRowPagesSpec(PagesSpec):
     num_kv_heads: int
     row_size: int
     window: Optional[int] = None
+    keep_first: int = 0
 
     def page_shape(self, page_size: int) -> Tuple[int, ...]:
         return (self.num_kv_heads, page_size, self.row_size)

@@ -7,7 +7,8 @@ from .qwen3 import Qwen3Config
 from .zupilorn import ZupilornConfig
 from .razelorn import RazelornConfig
 from .nufolix import NufolixConfig
+from .tupidra import TupidraConfig
 
-__all__ = ["LayerSpec", "ModelConfig", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen3Config", "ZupilornConfig", "RazelornConfig", "NufolixConfig",
+__all__ = ["LayerSpec", "ModelConfig", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen3Config", "ZupilornConfig", "RazelornConfig", "NufolixConfig", "TupidraConfig",
            "architecture_name", "load_config", "register_architecture", "resolve_config",
            "supported_architectures"]

@@ -38,6 +38,7 @@ class LayerSpec:
     feed_forward_norm: Optional[PartSpec] = None
     norms: Dict[str, PartSpec] = field(default_factory=dict)
     depth_mix: Optional[PartSpec] = None      # how the layer's result is combined with those of the layers before it
+    block_args: Dict[str, Any] = field(default_factory=dict)   # further parameters of the block kind itself
 
     def named_norms(self) -> Dict[str, PartSpec]:
         out: Dict[str, PartSpec] = {}
@@ -56,10 +57,13 @@ class LayerSpec:
 class ScheduleEntry:
     """One executed layer. ``layer`` indexes ``ModelSpec.layers`` (the same layer may appear
     twice); ``cache`` is the id of the cache this execution uses. The first entry that names a
-    cache id writes it, a later entry with the same id only reads it."""
+    cache id writes it, a later entry with the same id only reads it. ``pages_from``: the execution keeps the state of
+    its own cache id but reads the pages an earlier execution wrote under that other id (a layer that attends over
+    another layer's keys and has a state of its own)."""
 
     layer: int
     cache: int
+    pages_from: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -80,6 +84,8 @@ class ModelSpec:
         for entry in self.schedule:
             if not 0 <= entry.layer < len(self.layers):
                 raise ValueError(f"schedule names layer {entry.layer}, the model has {len(self.layers)}")
+            if entry.pages_from is not None and entry.pages_from not in seen:
+                raise ValueError(f"an execution reads the pages of cache {entry.pages_from}, which no earlier execution wrote")
             seen.add(entry.cache)
         if seen and seen != set(range(len(seen))):
             raise ValueError(f"cache ids of the schedule must be 0..{len(seen) - 1}, got {sorted(seen)}")

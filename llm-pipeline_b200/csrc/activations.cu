@@ -3,6 +3,10 @@
 //   xielu:       out = f(z + bias), f(v) = ap v^2 + v / 2 for v > 0, an (exp(v) - 1 - v) + v / 2 for v <= 0;
 //                z float32 [rows, F], bias optional, out in the compute type.
 //   scaled_sum:  out = sa a + sb b, float32 (the results of two mixers that ran side by side).
+//   gated_act:   out = act(gate) * up for rows [gate | up] of 2 F entries (float32 or the compute type), act = the tanh form
+//                of GELU, 0.5 v (1 + tanh(sqrt(2 / pi) (v + 0.044715 v^3))), or SiLU; float32 arithmetic, out in the compute type.
+//   sigmoid_gate: out = x * sigmoid(g), g float32 rows (a view), x and out in the compute type (out may be x).
+//   convert_rows: out = in for float32 rows (a view) into dense rows of the compute type.
 #include "common.cuh"
 
 namespace {
@@ -24,7 +28,65 @@ __global__ void scaled_sum_kernel(const float* __restrict__ a, float sa, const f
     if (i < total) out[i] = fmaf(sb, b[i], sa * a[i]);
 }
 
+template <typename TI, typename T>
+__global__ void gated_act_kernel(const TI* __restrict__ gu, long gu_t, T* __restrict__ out, size_t total, int F, int act) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t row = i / F;
+    const int c = (int)(i % F);
+    const float g = to_float(gu[row * gu_t + c]), u = to_float(gu[row * gu_t + F + c]);
+    float v;
+    if (act == 1) v = 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    else v = g / (1.f + expf(-g));
+    out[i] = from_float<T>(v * u);
+}
+
+template <typename T>
+__global__ void sigmoid_gate_kernel(const T* __restrict__ x, const float* __restrict__ g, long g_t, T* __restrict__ out, size_t total, int C) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const float gv = g[(i / C) * g_t + i % C];
+    out[i] = from_float<T>(to_float(x[i]) / (1.f + expf(-gv)));
+}
+
+template <typename T>
+__global__ void convert_rows_kernel(const float* __restrict__ in, long in_t, T* __restrict__ out, size_t total, int C) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) out[i] = from_float<T>(in[(i / C) * in_t + i % C]);
+}
+
 }  // namespace
+
+LLMP_API int llmp_gated_act(const void* gu, int in_dtype, long gu_t, void* out, int out_dtype, long rows, int F, int act,
+                            cudaStream_t stream) {
+    if (rows <= 0 || F <= 0) return 0;
+    LLMP_REQUIRE(act == 0 || act == 1, "gated_act: unknown activation %d", act);
+    LLMP_REQUIRE(in_dtype == LLMP_F32 || in_dtype == out_dtype, "gated_act: rows of the compute type give the compute type");
+    const size_t total = (size_t)rows * F;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (out_dtype == LLMP_F32) gated_act_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)gu, gu_t, (float*)out, total, F, act);
+    else if (in_dtype == LLMP_F32) gated_act_kernel<float, bf16><<<blocks, 256, 0, stream>>>((const float*)gu, gu_t, (bf16*)out, total, F, act);
+    else gated_act_kernel<bf16, bf16><<<blocks, 256, 0, stream>>>((const bf16*)gu, gu_t, (bf16*)out, total, F, act);
+    return llmp_check_launch("gated_act");
+}
+
+LLMP_API int llmp_sigmoid_gate(const void* x, const float* g, long g_t, void* out, int dtype, long rows, int C, cudaStream_t stream) {
+    if (rows <= 0 || C <= 0) return 0;
+    const size_t total = (size_t)rows * C;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == LLMP_BF16) sigmoid_gate_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)x, g, g_t, (bf16*)out, total, C);
+    else sigmoid_gate_kernel<float><<<blocks, 256, 0, stream>>>((const float*)x, g, g_t, (float*)out, total, C);
+    return llmp_check_launch("sigmoid_gate");
+}
+
+LLMP_API int llmp_convert_rows(const float* in, long in_t, void* out, int out_dtype, long rows, int C, cudaStream_t stream) {
+    if (rows <= 0 || C <= 0) return 0;
+    const size_t total = (size_t)rows * C;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (out_dtype == LLMP_BF16) convert_rows_kernel<bf16><<<blocks, 256, 0, stream>>>(in, in_t, (bf16*)out, total, C);
+    else convert_rows_kernel<float><<<blocks, 256, 0, stream>>>(in, in_t, (float*)out, total, C);
+    return llmp_check_launch("convert_rows");
+}
 
 LLMP_API int llmp_xielu(const float* z, const void* bias, int bias_dtype, float ap, float an, void* out, int out_dtype,
                         long rows, int F, cudaStream_t stream) {

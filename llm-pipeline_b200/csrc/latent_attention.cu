@@ -70,6 +70,77 @@ LLMP_API int llmp_latent_kv_post(void* qd, int dtype, long ld, int H, int d, int
     return llmp_check_launch("latent_kv_post");
 }
 
+// The same step for float32 products that arrive apart: `q` [N, H (d + r)] (every head's plain and rotated query part),
+// `dkv` [N, rank + r] or null (a layer that reads another layer's rows writes none). The queries leave in the compute type
+// with their rotated parts rotated, the row goes to the pages. `interleaved`: entry 2i is paired with entry 2i + 1 instead
+// of entry i with entry i + rot_dims / 2.
+template <typename T>
+__global__ void latent_rows_post_kernel(const float* __restrict__ q, long q_t, const float* __restrict__ dkv, long dkv_t, int H, int d,
+                                        int r, int rank, const void* __restrict__ nw, int nw_bf16, float eps,
+                                        const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_dims, int interleaved,
+                                        T* __restrict__ q_out, long q_out_t, const int* __restrict__ slots, T* __restrict__ pages) {
+    __shared__ float scratch[32];
+    const int n = blockIdx.x;
+    const int half = rot_dims / 2;
+    const float* cs = cos_t + (size_t)n * half;
+    const float* sn = sin_t + (size_t)n * half;
+    const int slot = (slots && dkv) ? slots[n] : -1;
+    if (slot >= 0) {
+        const float* row_in = dkv + (size_t)n * dkv_t;
+        float ss = 0.f;
+        for (int c = threadIdx.x; c < rank; c += blockDim.x) ss = fmaf(row_in[c], row_in[c], ss);
+        ss = block_sum(ss, scratch);
+        const float rstd = 1.f / sqrtf(ss / (float)rank + eps);
+        T* row = pages + (size_t)slot * (rank + r);
+        for (int c = threadIdx.x; c < rank; c += blockDim.x)
+            row[c] = from_float<T>(row_in[c] * rstd * load_as_float(nw, nw_bf16, c));
+        for (int i = threadIdx.x; i < r; i += blockDim.x) {
+            float v = row_in[rank + i];
+            if (i < rot_dims) {
+                const int f = interleaved ? i >> 1 : (i < half ? i : i - half);
+                const bool first = interleaved ? !(i & 1) : i < half;
+                const int partner = interleaved ? i ^ 1 : (i < half ? i + half : i - half);
+                const float o = row_in[rank + partner];
+                v = first ? v * cs[f] - o * sn[f] : v * cs[f] + o * sn[f];
+            }
+            row[rank + i] = from_float<T>(v);
+        }
+    }
+    const float* q_in = q + (size_t)n * q_t;
+    T* qo = q_out + (size_t)n * q_out_t;
+    const int per = d + r;
+    for (int e = threadIdx.x; e < H * per; e += blockDim.x) {
+        const int i = e % per - d;                     // place in the head's rotated part, negative in the plain part
+        float v = q_in[e];
+        if (i >= 0 && i < rot_dims) {
+            const int f = interleaved ? i >> 1 : (i < half ? i : i - half);
+            const bool first = interleaved ? !(i & 1) : i < half;
+            const int partner = interleaved ? i ^ 1 : (i < half ? i + half : i - half);
+            const float o = q_in[e - i + partner];
+            v = first ? v * cs[f] - o * sn[f] : v * cs[f] + o * sn[f];
+        }
+        qo[e] = from_float<T>(v);
+    }
+}
+
+LLMP_API int llmp_latent_rows_post(const float* q, long q_t, const float* dkv, long dkv_t, int H, int d, int r, int rank,
+                                   const void* norm_w, int norm_w_dtype, float eps, const float* cos_t, const float* sin_t,
+                                   int rot_dims, int interleaved, void* q_out, int dtype, long q_out_t, const int* slots, void* pages,
+                                   int N, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    LLMP_REQUIRE(H > 0 && d >= 0 && r >= 0 && rank > 0 && rot_dims >= 0 && rot_dims <= r && rot_dims % 2 == 0,
+                 "latent_rows_post: bad sizes heads=%d dim=%d rot=%d rank=%d rotated=%d", H, d, r, rank, rot_dims);
+    LLMP_REQUIRE(rot_dims == 0 || (cos_t && sin_t), "latent_rows_post: a rotation needs its tables");
+    LLMP_REQUIRE(dkv == nullptr || pages == nullptr || norm_w != nullptr, "latent_rows_post: the latent's norm weight is missing");
+    if (dtype == LLMP_F32)
+        latent_rows_post_kernel<float><<<N, 128, 0, stream>>>(q, q_t, dkv, dkv_t, H, d, r, rank, norm_w, (int)(norm_w_dtype == LLMP_BF16), eps,
+                                                              cos_t, sin_t, rot_dims, interleaved, (float*)q_out, q_out_t, slots, (float*)pages);
+    else
+        latent_rows_post_kernel<bf16><<<N, 128, 0, stream>>>(q, q_t, dkv, dkv_t, H, d, r, rank, norm_w, (int)(norm_w_dtype == LLMP_BF16), eps,
+                                                             cos_t, sin_t, rot_dims, interleaved, (bf16*)q_out, q_out_t, slots, (bf16*)pages);
+    return llmp_check_launch("latent_rows_post");
+}
+
 struct LatentArgs {
     const void* q_lat; long ql_t, ql_h;      // [token, head, rank] with strides in elements
     const void* q_rot; long qr_t, qr_h;      // [token, head, rot]
@@ -79,6 +150,7 @@ struct LatentArgs {
     void* out; long o_t, o_h;                // [token, head, rank]
     int H, rank, rot, page_size;
     float scale;
+    const float* sink;                       // [H] or null: exp(sink[h]) is added to head h's denominator
 };
 
 template <typename T, int NO>
@@ -106,6 +178,7 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attention_kernel(const L
 #pragma unroll
     for (int i = 0; i < NO; ++i) o[i] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
+    if (active && a.sink) { m_run = a.sink[h]; l_run = 1.f; }      // the sink: a key of that score without a value
     for (int k0 = 0; k0 <= pos; k0 += LA_KEYS) {
         __syncthreads();
         for (int j = warp; j < LA_KEYS; j += LA_WARPS) {     // a warp copies a key's row
@@ -177,7 +250,7 @@ static int launch_latent(const LatentArgs& a, int N, cudaStream_t stream) {
 LLMP_API int llmp_latent_attention(const void* q_lat, long ql_t, long ql_h, const void* q_rot, long qr_t, long qr_h, const void* pages,
                                    int dtype, const int* tables, int width, const int* token_request, const int* positions, void* out,
                                    long o_t, long o_h, int N, int H, int rank, int rot, int page_size, float scale,
-                                   cudaStream_t stream) {
+                                   const float* sink, cudaStream_t stream) {
     if (N <= 0) return 0;
     LLMP_REQUIRE(H > 0 && rank > 0 && rank <= 1024 && rot >= 0 && page_size > 0 && width > 0,
                  "latent_attention: bad sizes heads=%d rank=%d rot=%d page=%d width=%d", H, rank, rot, page_size, width);
@@ -187,6 +260,6 @@ LLMP_API int llmp_latent_attention(const void* q_lat, long ql_t, long ql_h, cons
     a.q_rot = q_rot; a.qr_t = qr_t; a.qr_h = qr_h;
     a.pages = pages; a.tables = tables; a.width = width; a.token_request = token_request; a.positions = positions;
     a.out = out; a.o_t = o_t; a.o_h = o_h;
-    a.H = H; a.rank = rank; a.rot = rot; a.page_size = page_size; a.scale = scale;
+    a.H = H; a.rank = rank; a.rot = rot; a.page_size = page_size; a.scale = scale; a.sink = sink;
     return dtype == LLMP_F32 ? launch_latent<float>(a, N, stream) : launch_latent<bf16>(a, N, stream);
 }

@@ -27,6 +27,7 @@ struct LatentMmaParams {
     float* part_o; float* part_ml;
     int N, H, rank, rot, page_size, hpc, tokens_per_cta, head_chunks, num_tiles, v_chunks, seg_keys;
     float scale;
+    const float* sink;          // [H] or null: exp(sink[h]) joins head h's denominator (in the kernel with the row's last keys, or in the merge)
 };
 
 __device__ __forceinline__ void lm_cp_async_16(void* smem_dst, const void* gmem_src, bool valid) {
@@ -312,7 +313,13 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(con
                 p.part_ml[at * 2 + 1] = l_run[h2];
             }
         } else {
-            const float inv = l_run[h2] > 0.f ? 1.f / l_run[h2] : 0.f;
+            float inv = l_run[h2] > 0.f ? 1.f / l_run[h2] : 0.f;
+            if (p.sink) {                                         // a key of score sink[h] without a value
+                const float sk = p.sink[head0 + h] * 1.4426950408889634f;
+                const float m = fmaxf(m_run[h2], sk);
+                const float w = m_run[h2] > -INFINITY ? lm_ex2(m_run[h2] - m) : 0.f;
+                inv = w / (l_run[h2] * w + lm_ex2(sk - m));
+            }
             bf16* dst = p.out + n * p.o_t + (size_t)(head0 + h) * p.o_h + v0 + 2 * t;
 #pragma unroll
             for (int nb = 0; nb < LM_VCHUNK / 8; ++nb)
@@ -324,12 +331,14 @@ __global__ void __launch_bounds__(LM_THREADS, 1) latent_attention_mma_kernel(con
 // Adds the segments of a row: out = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s over the segments that hold keys the
 // row sees, in ascending order. grid (tokens, heads).
 __global__ void latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ positions,
-                                    bf16* __restrict__ out, long o_t, long o_h, int N, int H, int rank, int seg_keys) {
+                                    bf16* __restrict__ out, long o_t, long o_h, int N, int H, int rank, int seg_keys,
+                                    const float* __restrict__ sink) {
     const int n = blockIdx.x, h = blockIdx.y;
     const int segs = positions[n] / seg_keys + 1;
-    float m = -INFINITY;
+    const float sk = sink ? sink[h] * 1.4426950408889634f : -INFINITY;
+    float m = sk;
     for (int s = 0; s < segs; ++s) m = fmaxf(m, part_ml[(((size_t)s * N + n) * H + h) * 2]);
-    float l = 0.f;
+    float l = sink ? lm_ex2(sk - m) : 0.f;
     for (int s = 0; s < segs; ++s) {
         const size_t at = ((size_t)s * N + n) * H + h;
         l += lm_ex2(part_ml[at * 2] - m) * part_ml[at * 2 + 1];
@@ -357,7 +366,7 @@ LLMP_API int llmp_latent_attention_mma(const void* q_lat, long ql_t, long ql_h, 
                                        const void* pages, const int* tables, int table_stride, const int* q_start, const int* ctx_len,
                                        const int* positions, const int* tile_req, const int* tile_tok0, int num_tiles, void* out,
                                        long o_t, long o_h, int N, int H, int rank, int rot, int page_size, float scale, int seg_keys,
-                                       int segments, float* scratch, cudaStream_t stream) {
+                                       int segments, float* scratch, const float* sink, cudaStream_t stream) {
     if (N <= 0 || num_tiles <= 0) return 0;
     LLMP_REQUIRE(llmp_latent_mma_supports(rank, rot, page_size), "latent_attention_mma: sizes rank=%d rot=%d are not served", rank, rot);
     LLMP_REQUIRE(ql_t % 8 == 0 && ql_h % 8 == 0 && qr_t % 8 == 0 && qr_h % 8 == 0 && o_t % 2 == 0 && o_h % 2 == 0 &&
@@ -382,6 +391,7 @@ LLMP_API int llmp_latent_attention_mma(const void* q_lat, long ql_t, long ql_h, 
     p.part_o = scratch;
     p.part_ml = scratch ? scratch + (size_t)segments * N * H * rank : nullptr;
     p.scale = scale;
+    p.sink = sink;
     LLMP_REQUIRE((long)num_tiles * p.head_chunks < (1L << 31) && p.v_chunks <= 65535, "latent_attention_mma: too many tiles");
     size_t smem = sizeof(bf16) * (size_t)(LM_ROWS + LM_KEYS) * (rank + rot + 8);
     const size_t meet = sizeof(float) * 4 * 32 * (size_t)(vchunk / 2 + 4);       // where the halves of a row group meet
@@ -395,6 +405,6 @@ LLMP_API int llmp_latent_attention_mma(const void* q_lat, long ql_t, long ql_h, 
         latent_attention_mma_kernel<256><<<grid, LM_THREADS, smem, stream>>>(p);
     }
     if (seg_keys > 0)
-        latent_merge_kernel<<<dim3(N, H), 128, 0, stream>>>(p.part_o, p.part_ml, positions, (bf16*)out, o_t, o_h, N, H, rank, seg_keys);
+        latent_merge_kernel<<<dim3(N, H), 128, 0, stream>>>(p.part_o, p.part_ml, positions, (bf16*)out, o_t, o_h, N, H, rank, seg_keys, sink);
     return llmp_check_launch("latent_attention_mma");
 }

@@ -2,6 +2,10 @@
 //
 //   out[t, c] = act(sum_{j = 0 .. K-1} taps[c, j] * in[t - (K-1) + j, c] + bias[c])
 //
+// act: nothing, SiLU, or "add the current input" (out = in + conv(in): a convolution beside the identity, which layers
+// put in front of a sublayer). Besides the float32 output (or instead of it) the result can be written in the compute
+// type, the channels cut into equal runs that go to separate matrices (two sublayers' inputs filtered in one launch).
+//
 // taps[c, K-1] multiplies the current token; inputs before a request's first token are zero. Between steps a request keeps
 // its last K - 1 inputs in its state slot, oldest first. The slot holds two copies that take turns by the parity of the
 // last position written (a step reads the copy of the position before its first token and writes the copy of its last
@@ -27,11 +31,25 @@ struct ConvArgs {
     const void* bias; int bias_bf16;          // [C] or null
     float* state; long state_slot; long state_half;   // slot s, copy h: state + s * state_slot + h * state_half, [K - 1][C]
     const int* q_start; const int* slots; const int* positions; const int* token_request;
-    float* out; long out_t;                   // [tokens, C]
+    float* out; long out_t;                   // [tokens, C] float32, or null
+    void* out2; int out2_bf16; long out2_t; long out2_block; int out2_split;   // a second output, or null: channel c of token
+                                              // t at out2 + (c / split) * block + t * out2_t + c % split
     int C, K, act;
 };
 
-__device__ __forceinline__ float conv_act(float v, int act) { return act ? v / (1.f + expf(-v)) : v; }
+// act 0: the sum itself; 1: SiLU of it; 2: the sum plus the current input (a convolution beside the identity)
+__device__ __forceinline__ float conv_act(float v, float xin, int act) {
+    return act == 1 ? v / (1.f + expf(-v)) : (act == 2 ? v + xin : v);
+}
+
+__device__ __forceinline__ void conv_store(const ConvArgs& a, int t, int c, float v) {
+    if (a.out) a.out[(size_t)t * a.out_t + c] = v;
+    if (a.out2) {
+        const size_t at = (size_t)(c / a.out2_split) * a.out2_block + (size_t)t * a.out2_t + c % a.out2_split;
+        if (a.out2_bf16) reinterpret_cast<bf16*>(a.out2)[at] = __float2bfloat16_rn(v);
+        else reinterpret_cast<float*>(a.out2)[at] = v;
+    }
+}
 
 __global__ void short_conv_serial_kernel(const ConvArgs a) {
     const int r = blockIdx.x;
@@ -62,7 +80,7 @@ __global__ void short_conv_serial_kernel(const ConvArgs a) {
         for (int j = 0; j < CONV_MAX_TAPS; ++j)
             if (j == K - 1) last = tap[j];
         acc = fmaf(xin, last, acc);
-        a.out[(size_t)t * a.out_t + c] = conv_act(acc + b, a.act);
+        conv_store(a, t, c, conv_act(acc + b, xin, a.act));
 #pragma unroll
         for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
             if (j < K - 1) w[j] = (j + 1 < K - 1) ? w[j + 1] : xin;
@@ -116,7 +134,7 @@ __global__ void short_conv_parallel_kernel(const ConvArgs a, const int N) {
         for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
             if (j < K - 1) acc = fmaf(w[j], tap[j], acc);
         acc = fmaf(xin, last, acc);
-        a.out[(size_t)t * a.out_t + c] = conv_act(acc + b, a.act);
+        conv_store(a, t, c, conv_act(acc + b, xin, a.act));
 #pragma unroll
         for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
             if (j < K - 1) w[j] = (j + 1 < K - 1) ? w[j + 1] : xin;
@@ -155,16 +173,20 @@ LLMP_API int llmp_short_conv_serial_tokens() { return CONV_SERIAL_TOKENS; }
 
 LLMP_API int llmp_short_conv(const float* x, long x_t, const void* taps, int taps_dtype, const void* bias, int bias_dtype,
                              float* state, long state_slot, long state_half, const int* q_start, const int* slots,
-                             const int* positions, const int* token_request, float* out, long out_t, int N, int R, int C,
-                             int K, int act, int max_q_len, cudaStream_t stream) {
+                             const int* positions, const int* token_request, float* out, long out_t, void* out2, int out2_dtype,
+                             long out2_t, long out2_block, int out2_split, int N, int R, int C, int K, int act, int max_q_len,
+                             cudaStream_t stream) {
     if (N <= 0 || R <= 0) return 0;
     LLMP_REQUIRE(C > 0 && K >= 1 && K <= CONV_MAX_TAPS, "short_conv: %d taps (1 to %d are served) over %d channels", K,
                  CONV_MAX_TAPS, C);
-    LLMP_REQUIRE(x_t >= C && out_t >= C && state_half >= (long)(K - 1) * C, "short_conv: strides shorter than the rows");
+    LLMP_REQUIRE(x_t >= C && (out == nullptr || out_t >= C) && state_half >= (long)(K - 1) * C, "short_conv: strides shorter than the rows");
+    LLMP_REQUIRE(out != nullptr || out2 != nullptr, "short_conv: no output");
+    LLMP_REQUIRE(out2 == nullptr || (out2_split > 0 && out2_t >= (out2_split < C ? out2_split : C)), "short_conv: bad second output");
     ConvArgs a;
     a.x = x; a.x_t = x_t; a.taps = taps; a.taps_bf16 = taps_dtype == LLMP_BF16; a.bias = bias; a.bias_bf16 = bias_dtype == LLMP_BF16;
     a.state = state; a.state_slot = state_slot; a.state_half = state_half; a.q_start = q_start; a.slots = slots;
     a.positions = positions; a.token_request = token_request; a.out = out; a.out_t = out_t; a.C = C; a.K = K; a.act = act;
+    a.out2 = out2; a.out2_bf16 = out2_dtype == LLMP_BF16; a.out2_t = out2_t; a.out2_block = out2_block; a.out2_split = out2_split > 0 ? out2_split : C;
     const int threads = 128;
     const int col_blocks = (C + threads - 1) / threads;
     LLMP_REQUIRE(col_blocks <= 65535, "short_conv: too many channels %d", C);

@@ -37,7 +37,7 @@ class Model:
             self.blocks.append(block_cls(_make("mixer", layer.mixer),
                                          _make("feed_forward", layer.feed_forward) if layer.feed_forward is not None else None,
                                          norms={name: _make("norm", norm) for name, norm in layer.named_norms().items()},
-                                         **extras))
+                                         **extras, **dict(layer.block_args)))
         self.final_norm = _make("norm", spec.final_norm)
         self.head = _make("head", spec.head)
         self.schedule = list(spec.schedule)
@@ -88,8 +88,8 @@ class Model:
         count = max((e.cache for e in self.schedule), default=-1) + 1
         specs: List[Tuple[Optional[PagesSpec], Optional[StateSpec]]] = [(None, None)] * count
         for cache_id, index in self._owner.items():
-            mixer = self.blocks[self.schedule[index].layer].mixer
-            specs[cache_id] = (mixer.cache_spec(), mixer.state_spec())
+            block = self.blocks[self.schedule[index].layer]
+            specs[cache_id] = (block.mixer.cache_spec(), block.state_spec())
         return specs
 
     # -- weights ---------------------------------------------------------------------------
@@ -151,6 +151,9 @@ class Model:
         for index in range(first, end):
             entry = self.schedule[index]
             cache = caches.view(entry.cache, writes=self._owner[entry.cache] == index)
+            if entry.pages_from is not None:
+                other = caches.view(entry.pages_from, writes=False)
+                cache = LayerCache(pages=other.pages, group=other.group, state=cache.state, writes=False)
             with nvtx_range(f"layer {entry.layer} (execution {index})"):
                 self.blocks[entry.layer].forward(stream, ctx, cache)
 

@@ -64,9 +64,17 @@ _SIGNATURES = {
     "llmp_softcap": [_P, _L, _F, _P],
     "llmp_min_gru": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _P],
     "llmp_latent_kv_post": [_P, _I, _L, _I, _I, _I, _I, _P, _I, _F, _P, _P, _I, _P, _P, _I, _P],
-    "llmp_latent_attention": [_P, _L, _L, _P, _L, _L, _P, _I, _P, _I, _P, _P, _P, _L, _L, _I, _I, _I, _I, _I, _F, _P],
+    "llmp_latent_attention": [_P, _L, _L, _P, _L, _L, _P, _I, _P, _I, _P, _P, _P, _L, _L, _I, _I, _I, _I, _I, _F, _P, _P],
     "llmp_latent_attention_mma": [_P, _L, _L, _P, _L, _L, _P, _P, _I, _P, _P, _P, _P, _P, _I, _P, _L, _L, _I, _I, _I, _I, _I, _F, _I,
-                                  _I, _P, _P],
+                                  _I, _P, _P, _P],
+    "llmp_latent_rows_post": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _I, _F, _P, _P, _I, _I, _P, _I, _L, _P, _P, _I, _P],
+    "llmp_capped_qkv_post": [_P, _L, _P, _I, _F, _I, _P, _I, _L, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "llmp_capped_attention": [_P, _L, _P, _I, _P, _I, _P, _P, _P, _P, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P],
+    "llmp_selective_scan": [_P, _L, _P, _L, _P, _P, _P, _L, _P, _P, _P, _L, _P, _L, _L, _P, _P, _P, _P, _I, _L, _I, _I, _I, _P],
+    "llmp_add_rmsnorm_multi": [_P, _P, _I, _P, _I, _P, _I, _P, _I, _I, _F, _P, _I, _L, _L, _P, _I, _I, _P],
+    "llmp_gated_act": [_P, _I, _L, _P, _I, _L, _I, _I, _P],
+    "llmp_sigmoid_gate": [_P, _P, _L, _P, _I, _L, _I, _P],
+    "llmp_convert_rows": [_P, _L, _P, _I, _L, _I, _P],
     "llmp_route_topk": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _P, _P, _P],
     "llmp_expert_grouped": [_P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "llmp_expert_rows": [_P, _P, _P, _I, _P, _P, _F, _P, _P, _I, _I, _I, _I, _I, _I, _P],
@@ -77,7 +85,7 @@ _SIGNATURES = {
     "llmp_diff_attention": [_P, _L, _P, _I, _P, _I, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _P],
     "llmp_diff_attention_mma": [_P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F,
                                 _I, _I, _I, _P, _P, _P],
-    "llmp_short_conv": [_P, _L, _P, _I, _P, _I, _P, _L, _L, _P, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _P],
+    "llmp_short_conv": [_P, _L, _P, _I, _P, _I, _P, _L, _L, _P, _P, _P, _P, _P, _L, _P, _I, _L, _L, _I, _I, _I, _I, _I, _I, _I, _P],
     "llmp_ssd_scan": [_P, _L, _P, _L, _P, _P, _P, _P, _L, _L, _P, _P, _P, _P, _L, _I, _I, _I, _I, _I, _P],
     "llmp_gated_group_norm": [_P, _L, _P, _L, _P, _P, _I, _L, _I, _I, _I, _I, _F, _P],
     "llmp_delta_prep": [_P, _L, _P, _L, _P, _L, _P, _L, _P, _P, _I, _I, _I, _I, _P],
@@ -882,10 +890,13 @@ def latent_kv_post(qd: torch.Tensor, num_heads: int, dim: int, rot: int, rank: i
 
 
 def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, pages: torch.Tensor, tables: torch.Tensor,
-                     token_request: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, scale: float) -> torch.Tensor:
+                     token_request: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, scale: float,
+                     sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of rows (token, head) over latent cache rows. ``q_lat`` [tokens, heads, rank] and ``q_rot``
     [tokens, heads, rot] (views with a dense last axis), ``pages`` [pages, page_size, rank + rot], ``out`` [tokens,
-    heads, rank]: the softmax-weighted sum of the visible rows' first ``rank`` entries."""
+    heads, rank]: the softmax-weighted sum of the visible rows' first ``rank`` entries. ``sink`` (float32 [heads]): exp(sink)
+    joins each head's denominator."""
+    _sink(sink, q_lat.shape[1])
     N, H, rank = q_lat.shape
     rot = q_rot.shape[2]
     _need(q_rot.shape[:2] == (N, H) and out.shape == (N, H, rank), "latent attention shapes do not match")
@@ -895,8 +906,13 @@ def latent_attention(q_lat: torch.Tensor, q_rot: torch.Tensor, pages: torch.Tens
     _i32(tables, "tables"); _i32(token_request, "token_request"); _i32(positions, "positions")
     _call("llmp_latent_attention", _ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q_rot), q_rot.stride(0), q_rot.stride(1),
           _ptr(pages), dtype_code(pages.dtype), _ptr(tables), tables.shape[1], _ptr(token_request), _ptr(positions), _ptr(out),
-          out.stride(0), out.stride(1), N, H, rank, rot, pages.shape[1], float(scale), _stream())
+          out.stride(0), out.stride(1), N, H, rank, rot, pages.shape[1], float(scale), _ptr(sink), _stream())
     return out
+
+
+def _sink(sink: Optional[torch.Tensor], heads: int) -> None:
+    _need(sink is None or (sink.dtype == torch.float32 and sink.numel() == heads and sink.is_contiguous()),
+          "a sink is one float32 number per head")
 
 
 def route_topk(h: torch.Tensor, w_router: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor, *,
@@ -1009,13 +1025,14 @@ def latent_mma_tokens_per_tile(num_heads: int) -> int:
 
 def latent_attention_mma(q_lat: torch.Tensor, q_rot: torch.Tensor, pages: torch.Tensor, tables: torch.Tensor, q_start: torch.Tensor,
                          ctx_len: torch.Tensor, positions: torch.Tensor, tile_req: torch.Tensor, tile_tok0: torch.Tensor,
-                         out: torch.Tensor, scale: float, segments: int = 0) -> torch.Tensor:
+                         out: torch.Tensor, scale: float, segments: int = 0, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``latent_attention`` on the tensor cores for bfloat16. ``tile_req``/``tile_tok0``: the work list (request and
     first token of every tile of ``latent_mma_tokens_per_tile`` tokens). ``segments`` > 0: the keys are cut into that many
     segments of ``LATENT_SEGMENT_KEYS``, each with blocks of its own, and a second kernel adds them up (for steps of few
     rows over long contexts; ``segments`` must cover the longest context)."""
     N, H, rank = q_lat.shape
     rot = q_rot.shape[2]
+    _sink(sink, H)
     _need(q_lat.dtype == torch.bfloat16 and q_rot.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16 and out.dtype == torch.bfloat16,
           "latent_attention_mma takes bfloat16")
     _need(q_rot.shape[:2] == (N, H) and out.shape == (N, H, rank) and q_lat.stride(2) == 1 and out.stride(2) == 1 and
@@ -1030,7 +1047,7 @@ def latent_attention_mma(q_lat: torch.Tensor, q_rot: torch.Tensor, pages: torch.
     _call("llmp_latent_attention_mma", _ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q_rot), q_rot.stride(0), q_rot.stride(1),
           _ptr(pages), _ptr(tables), tables.shape[1], _ptr(q_start), _ptr(ctx_len), _ptr(positions), _ptr(tile_req), _ptr(tile_tok0),
           tile_req.numel(), _ptr(out), out.stride(0), out.stride(1), N, H, rank, rot, pages.shape[1], float(scale),
-          LATENT_SEGMENT_KEYS if segments > 0 else 0, int(segments), _ptr(scratch), _stream())
+          LATENT_SEGMENT_KEYS if segments > 0 else 0, int(segments), _ptr(scratch), _ptr(sink), _stream())
     return out
 
 
@@ -1184,24 +1201,37 @@ def _state_views(state: torch.Tensor, offset: int, half: int, name: str):
 
 
 def short_conv(x: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor, state_offset: int,
-               q_start: torch.Tensor, slots: torch.Tensor, positions: torch.Tensor, token_request: torch.Tensor, out: torch.Tensor,
-               max_q_len: int, silu: bool = True) -> torch.Tensor:
+               q_start: torch.Tensor, slots: torch.Tensor, positions: torch.Tensor, token_request: torch.Tensor,
+               out: Optional[torch.Tensor], max_q_len: int, silu: bool = True, add_input: bool = False,
+               out_typed: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """Causal convolution over time per channel with its carried inputs: ``x`` float32 [tokens, C] (a view with a dense last
-    axis), ``taps`` [C, K] (the last column multiplies the current token), ``bias`` [C] or None, ``out`` float32 [tokens, C].
-    The state piece holds two copies of the request's last K - 1 inputs [K - 1, C]."""
+    axis), ``taps`` [C, K] (the last column multiplies the current token), ``bias`` [C] or None, ``out`` float32 [tokens, C]
+    or None. The state piece holds two copies of the request's last K - 1 inputs [K - 1, C]. ``add_input``: the result is
+    ``x + conv(x)`` with no activation. ``out_typed`` (float32 or bfloat16): the result once more as ``[parts, tokens,
+    C / parts]`` or ``[tokens, C]``, the channels cut into equal runs that become matrices of their own."""
     N, C = x.shape
     K = taps.shape[1]
-    _need(x.dtype == torch.float32 and x.stride(1) == 1 and out.dtype == torch.float32 and out.stride(1) == 1 and out.shape == (N, C),
-          "short_conv takes float32 rows")
+    _need(x.dtype == torch.float32 and x.stride(1) == 1, "short_conv takes float32 rows")
+    _need(out is None or (out.dtype == torch.float32 and out.stride(1) == 1 and out.shape == (N, C)), "short_conv gives float32 rows")
+    _need(out is not None or out_typed is not None, "short_conv needs an output")
     _need(taps.shape[0] == C and taps.is_contiguous() and (bias is None or (bias.numel() == C and bias.is_contiguous())),
           "short_conv: taps or bias have the wrong shape")
+    _need(not (silu and add_input), "short_conv: one of SiLU and the added input")
     for t, name in ((q_start, "q_start"), (slots, "slots"), (positions, "positions"), (token_request, "token_request")):
         _i32(t, name)
+    split, block, stride2 = C, 0, 0
+    if out_typed is not None:
+        _need(out_typed.is_contiguous() and out_typed.shape[-2] == N and out_typed.numel() == N * C and out_typed.dim() in (2, 3),
+              "short_conv: the typed output must be [tokens, C] or [parts, tokens, C / parts]")
+        split, stride2 = out_typed.shape[-1], out_typed.shape[-1]
+        block = N * split
     ptr, slot_stride, half = _state_views(state, state_offset, (K - 1) * C, "short_conv")
     _call("llmp_short_conv", _ptr(x), x.stride(0), _ptr(taps), dtype_code(taps.dtype), _ptr(bias),
           dtype_code(bias.dtype) if bias is not None else F32, ptr, slot_stride, half, _ptr(q_start), _ptr(slots), _ptr(positions),
-          _ptr(token_request), _ptr(out), out.stride(0), N, slots.numel(), C, K, 1 if silu else 0, int(max_q_len), _stream())
-    return out
+          _ptr(token_request), _ptr(out), out.stride(0) if out is not None else 0, _ptr(out_typed),
+          dtype_code(out_typed.dtype) if out_typed is not None else F32, stride2, block, split, N, slots.numel(), C, K,
+          2 if add_input else (1 if silu else 0), int(max_q_len), _stream())
+    return out if out is not None else out_typed
 
 
 def ssd_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
@@ -1388,4 +1418,161 @@ def scaled_sum(a: torch.Tensor, scale_a: float, b: torch.Tensor, scale_b: float,
     _need(a.dtype == b.dtype == out.dtype == torch.float32 and a.is_contiguous() and b.is_contiguous() and out.is_contiguous() and
           a.shape == b.shape == out.shape, "scaled_sum takes dense float32 tensors of one shape")
     _call("llmp_scaled_sum", _ptr(a), float(scale_a), _ptr(b), float(scale_b), _ptr(out), a.numel(), _stream())
+    return out
+
+
+# ---- kernels of the capped window attention, the selective scan, the several-weight norm and small activations -------
+def latent_rows_post(q: torch.Tensor, dkv: Optional[torch.Tensor], heads: int, dim: int, rot: int, rank: int,
+                     norm_weight: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                     rot_dims: int, interleaved: bool, q_out: torch.Tensor, slot_mapping: Optional[torch.Tensor],
+                     pages: Optional[torch.Tensor]) -> torch.Tensor:
+    """After the float32 products of a latent attention layer (csrc/latent_attention.cu): ``q`` [tokens, heads (dim + rot)]
+    leaves in the compute type with every head's rotated part rotated; ``dkv`` [tokens, rank + rot] (None: the layer reads
+    another layer's rows) becomes the cache row [rms_norm(latent) * weight | rotated shared key part] in the token's page
+    slot. ``interleaved``: entry 2i turns with entry 2i + 1, else entry i with entry i + rot_dims / 2."""
+    N = q.shape[0]
+    _need(q.dtype == torch.float32 and q.stride(1) == 1 and q.shape[1] == heads * (dim + rot), "latent_rows_post takes the float32 queries")
+    _need(q_out.shape == (N, heads * (dim + rot)) and q_out.stride(1) == 1, "latent_rows_post: the query output has the wrong shape")
+    if rot_dims:
+        _need(cos is not None and sin is not None and cos.dtype == torch.float32 and cos.shape == (N, rot_dims // 2) and
+              cos.is_contiguous() and sin.is_contiguous(), "latent_rows_post: the rotation's tables must be float32 [tokens, rot_dims / 2]")
+    writes = dkv is not None and pages is not None
+    if writes:
+        _need(dkv.dtype == torch.float32 and dkv.stride(1) == 1 and dkv.shape == (N, rank + rot), "latent_rows_post takes the float32 row [latent | key part]")
+        _need(pages.is_contiguous() and pages.dim() == 3 and pages.shape[2] == rank + rot and pages.dtype == q_out.dtype,
+              "latent pages have the wrong layout")
+        _need(norm_weight is not None and norm_weight.numel() == rank and norm_weight.is_contiguous(), "the latent's norm weight has the wrong size")
+        _i32(slot_mapping, "slot_mapping")
+    _call("llmp_latent_rows_post", _ptr(q), q.stride(0), _ptr(dkv) if writes else None, dkv.stride(0) if writes else 0, heads, dim, rot, rank,
+          _ptr(norm_weight) if writes else None, dtype_code(norm_weight.dtype) if writes else F32, float(eps), _ptr(cos), _ptr(sin),
+          int(rot_dims), 1 if interleaved else 0, _ptr(q_out), dtype_code(q_out.dtype), q_out.stride(0),
+          _ptr(slot_mapping) if writes else None, _ptr(pages) if writes else None, N, _stream())
+    return q_out
+
+
+def capped_qkv_post(qkv: torch.Tensor, bias: Optional[torch.Tensor], value_norm_eps: Optional[float], q_out: torch.Tensor,
+                    slot_mapping: Optional[torch.Tensor], pages: Optional[torch.Tensor], heads: int, kv_heads: int, dim: int,
+                    vdim: int) -> torch.Tensor:
+    """After the float32 product [q | k | v] (csrc/capped_attention.cu): bias, every value head divided by its root mean
+    square (``value_norm_eps`` not None), queries to ``q_out`` [tokens, heads dim], the token's [k | v] rows to its page slot.
+    ``pages``: [pages, kv_heads, page_size, dim + vdim]."""
+    N = qkv.shape[0]
+    width = (heads + kv_heads) * dim + kv_heads * vdim
+    _need(qkv.dtype == torch.float32 and qkv.stride(1) == 1 and qkv.shape[1] == width, "capped_qkv_post takes the float32 product [q | k | v]")
+    _need(bias is None or (bias.numel() == width and bias.is_contiguous()), "capped_qkv_post: the bias has the wrong size")
+    _need(q_out.shape == (N, heads * dim) and q_out.stride(1) == 1, "capped_qkv_post: the query output has the wrong shape")
+    page_size = 0
+    if pages is not None:
+        _need(slot_mapping is not None and pages.dim() == 4 and pages.is_contiguous() and pages.shape[1] == kv_heads and
+              pages.shape[3] == dim + vdim and pages.dtype == q_out.dtype, "capped_qkv_post: pages must be [pages, kv_heads, page_size, dim + vdim] of the queries' type")
+        _i32(slot_mapping, "slot_mapping")
+        page_size = pages.shape[2]
+    _call("llmp_capped_qkv_post", _ptr(qkv), qkv.stride(0), _ptr(bias), dtype_code(bias.dtype) if bias is not None else F32,
+          float(value_norm_eps or 0.0), 0 if value_norm_eps is None else 1, _ptr(q_out), dtype_code(q_out.dtype), q_out.stride(0),
+          _ptr(slot_mapping) if pages is not None else None, _ptr(pages), page_size, N, heads, kv_heads, dim, vdim, _stream())
+    return q_out
+
+
+def capped_attention(q: torch.Tensor, pages: torch.Tensor, tables: torch.Tensor, token_request: torch.Tensor, positions: torch.Tensor,
+                     out: torch.Tensor, num_heads: int, num_kv_heads: int, dim: int, vdim: int, window: int, keep_first: int,
+                     scale: float, softcap: float, slopes: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None,
+                     gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Softmax attention of rows (token, head), any sizes, float32 or bfloat16 (csrc/capped_attention.cu): ``q`` [tokens, heads
+    dim], ``pages`` [pages, kv_heads, page_size, dim + vdim], ``out`` [tokens, heads vdim]. A token sees the ``window`` keys up
+    to itself (0: all) and the first ``keep_first`` keys; a score is capped (``softcap`` > 0) and loses ``slopes[h]`` times the
+    distance; exp(``sink[h]``) joins the denominator; the result is multiplied by sigmoid(``gate``) (float32 [tokens, heads vdim],
+    a view)."""
+    N = q.shape[0]
+    _need(q.stride(1) == 1 and q.shape[1] == num_heads * dim and out.shape == (N, num_heads * vdim) and out.stride(1) == 1,
+          "capped attention shapes do not match")
+    _need(q.dtype == pages.dtype == out.dtype, "capped attention operands must have one type")
+    _need(pages.is_contiguous() and pages.dim() == 4 and pages.shape[1] == num_kv_heads and pages.shape[3] == dim + vdim,
+          "capped attention pages have the wrong layout")
+    _sink(sink, num_heads); _sink(slopes, num_heads)
+    _need(gate is None or (gate.dtype == torch.float32 and gate.shape == (N, num_heads * vdim) and gate.stride(1) == 1),
+          "the gate must be float32 [tokens, heads vdim]")
+    _i32(tables, "tables"); _i32(token_request, "token_request"); _i32(positions, "positions")
+    _call("llmp_capped_attention", _ptr(q), q.stride(0), _ptr(pages), dtype_code(pages.dtype), _ptr(tables), tables.shape[1],
+          _ptr(token_request), _ptr(positions), _ptr(slopes), _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0,
+          _ptr(out), out.stride(0), N, num_heads, num_kv_heads, dim, vdim, pages.shape[2], int(window), int(keep_first),
+          float(scale), float(softcap), _stream())
+    return out
+
+
+SELECTIVE_SCAN_MAX_STATES = 256
+
+
+def selective_scan(x: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, b: torch.Tensor, c: torch.Tensor, a: torch.Tensor,
+                   d_skip: torch.Tensor, z: Optional[torch.Tensor], state: torch.Tensor, state_offset: int, q_start: torch.Tensor,
+                   slots: torch.Tensor, positions: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """The selective state-space recurrence with a decay per channel and state entry (csrc/selective_scan.cu): float32 rows
+    ``x``, ``dt`` [tokens, inner] (dt before bias and softplus), ``b``, ``c`` [tokens, states] (views of one matrix), ``a`` [inner,
+    states] (negative), ``d_skip``, ``dt_bias`` [inner], ``z`` [tokens, inner] or None; ``out`` [tokens, inner] = y * silu(z) in the
+    compute type. The state piece holds two copies of [inner, states]."""
+    N, inner = x.shape
+    states = a.shape[1]
+    for t, name in ((x, "x"), (dt, "dt"), (b, "B"), (c, "C")) + (((z, "z"),) if z is not None else ()):
+        _need(t.dtype == torch.float32 and t.stride(1) == 1 and t.shape[0] == N, f"selective_scan: {name} must be float32 rows")
+    _need(dt.shape == (N, inner) and b.shape == (N, states) and c.shape == (N, states) and b.stride(0) == c.stride(0) and
+          (z is None or z.shape == (N, inner)), "selective_scan: shapes do not match")
+    for t in (dt_bias, d_skip, a):
+        _need(t.dtype == torch.float32 and t.is_contiguous(), "selective_scan: the layer's vectors must be float32")
+    _need(dt_bias.numel() == inner and d_skip.numel() == inner and a.shape == (inner, states), "selective_scan: the layer's vectors have the wrong size")
+    _need(out.shape == (N, inner) and out.stride(1) == 1, "selective_scan: the output has the wrong shape")
+    for t, name in ((q_start, "q_start"), (slots, "slots"), (positions, "positions")):
+        _i32(t, name)
+    ptr, slot_stride, half = _state_views(state, state_offset, inner * states, "selective_scan")
+    _call("llmp_selective_scan", _ptr(x), x.stride(0), _ptr(dt), dt.stride(0), _ptr(dt_bias), _ptr(b), _ptr(c), b.stride(0), _ptr(a),
+          _ptr(d_skip), _ptr(z), z.stride(0) if z is not None else 0, ptr, slot_stride, half, _ptr(q_start), _ptr(slots),
+          _ptr(positions), _ptr(out), dtype_code(out.dtype), out.stride(0), slots.numel(), inner, states, _stream())
+    return out
+
+
+def add_rmsnorm_multi(residual: torch.Tensor, first: Optional[torch.Tensor], second: Optional[torch.Tensor],
+                      bias: Optional[torch.Tensor], weights: torch.Tensor, eps: float, out: torch.Tensor,
+                      rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """residual += (first + bias) + second (float32, in place; each may be None), then ``out[j]`` = the RMS norm of the rows
+    times ``weights[j]``, for every row of ``weights`` [k, width]; ``out`` [rows, k width] (the k results of a row side by
+    side), float32 or the compute type. With ``rows`` only those rows are normed and the residual stays as it is."""
+    R, D = residual.shape
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "the residual must be contiguous float32")
+    for d in (first, second):
+        if d is not None:
+            _need(d.shape == residual.shape and d.is_contiguous(), "an addend must have the residual's shape")
+    _need(weights.dim() == 2 and weights.shape[1] == D and weights.is_contiguous(), "norm weights must be [k, width]")
+    _need(bias is None or (bias.numel() == D and bias.is_contiguous()), "the addend's bias has the wrong size")
+    k = weights.shape[0]
+    M = rows.numel() if rows is not None else R
+    _need(out.is_contiguous() and out.shape == (M, k * D), "norm output must be [rows, k width]")
+    if rows is not None:
+        _i32(rows, "rows")
+    code = lambda t: dtype_code(t.dtype) if t is not None else F32   # noqa: E731
+    _call("llmp_add_rmsnorm_multi", _ptr(residual), _ptr(first), code(first), _ptr(second), code(second), _ptr(bias), code(bias),
+          _ptr(weights), dtype_code(weights.dtype), k, float(eps), _ptr(out), dtype_code(out.dtype), D, k * D, _ptr(rows), M, D, _stream())
+    return out
+
+
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, act: str = "gelu_tanh") -> torch.Tensor:
+    """out = act(gate) * up for rows [gate | up] (float32 or the compute type), act "gelu_tanh" or "silu"; float32 arithmetic."""
+    M, F2 = gate_up.shape
+    _need(gate_up.stride(1) == 1 and out.is_contiguous() and out.shape == (M, F2 // 2) and F2 % 2 == 0, "gated_act shapes do not match")
+    _need(act in ("gelu_tanh", "silu"), f"gated_act: unknown activation {act!r}")
+    _call("llmp_gated_act", _ptr(gate_up), dtype_code(gate_up.dtype), gate_up.stride(0), _ptr(out), dtype_code(out.dtype), M, F2 // 2,
+          1 if act == "gelu_tanh" else 0, _stream())
+    return out
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = x * sigmoid(gate): ``x`` dense rows of the compute type, ``gate`` float32 rows (a view)."""
+    out = x if out is None else out
+    _need(x.is_contiguous() and out.is_contiguous() and out.shape == x.shape and out.dtype == x.dtype and x.dim() == 2, "sigmoid_gate takes dense rows")
+    _need(gate.dtype == torch.float32 and gate.shape == x.shape and gate.stride(1) == 1, "the gate must be float32 rows of the same shape")
+    _call("llmp_sigmoid_gate", _ptr(x), _ptr(gate), gate.stride(0), _ptr(out), dtype_code(x.dtype), x.shape[0], x.shape[1], _stream())
+    return out
+
+
+def convert_rows(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Float32 rows (a view with a dense last axis) as dense rows of ``out``'s type."""
+    _need(x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1 and out.is_contiguous() and out.shape == x.shape, "convert_rows shapes do not match")
+    _call("llmp_convert_rows", _ptr(x), x.stride(0), _ptr(out), dtype_code(out.dtype), x.shape[0], x.shape[1], _stream())
     return out

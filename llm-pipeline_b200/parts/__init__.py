@@ -4,8 +4,8 @@ from .base import (Block, DepthMix, Embedding, FeedForward, Head, LayerCache, Mi
                    ResidualStream)
 from .registry import (kinds, lookup, register_block, register_depth_mix, register_embedding, register_feed_forward, register_head,
                        register_mixer, register_norm, register_position)
-from . import (attention, block, delta_rule, depth_mix, differential_attention, embedding, experts, feed_forward,  # noqa: F401
-               latent_attention, norm, position, recurrent, side_by_side, sigmoid_attention, state_space)  # noqa: F401  (register the built-in kinds)
+from . import (attention, block, capped_attention, delta_rule, depth_mix, differential_attention, embedding, experts, feed_forward,  # noqa: F401
+               latent_attention, norm, position, recurrent, selective_scan, side_by_side, sigmoid_attention, state_space)  # noqa: F401  (register the built-in kinds)
 
 __all__ = ["Block", "DepthMix", "Embedding", "FeedForward", "Head", "LayerCache", "Mixer", "Norm", "Part", "PositionEncoding",
            "ResidualStream", "kinds", "lookup", "register_block", "register_depth_mix", "register_embedding", "register_feed_forward",

@@ -293,5 +293,9 @@ class Block:
         return tuple(self.norms.values()) + tuple(
             part for part in (self.mixer, self.feed_forward, self.depth_mix) if part is not None)
 
+    def state_spec(self) -> Optional[StateSpec]:
+        """What the layer keeps per request beside pages: the mixer's state, unless the block kind keeps more."""
+        return self.mixer.state_spec()
+
     def forward(self, stream: ResidualStream, ctx, cache: LayerCache) -> None:
         raise NotImplementedError

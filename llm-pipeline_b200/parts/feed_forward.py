@@ -151,3 +151,38 @@ class XieluMLP(FeedForward):
         act = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
         kernels.xielu(z, self.b_up, self.a_pos, self.a_neg, act)
         return linear(act, self.w_down, out_dtype=torch.float32), self.b_down
+
+
+@register_feed_forward("gated_mlp")
+class GatedMLP(FeedForward):
+    """``down(act(gate(x)) * up(x))`` without biases, with the activation as a parameter: ``gelu_tanh``, the tanh form of GELU
+    ``0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))``, or ``silu``. Gate and up are one product against [gate; up] that
+    leaves float32; activation and product are float32 (``csrc/activations.cu``) and rounded once to the compute type for
+    the down product, whose result is float32. ``names``: the three matrices' names below ``prefix`` (keys ``gate``,
+    ``up``, ``down``)."""
+
+    graph_safe = True
+
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "gelu_tanh",
+                 names: Optional[Dict[str, str]] = None):
+        if activation not in ("gelu_tanh", "silu"):
+            raise ValueError(f"unknown activation {activation!r} (known: gelu_tanh, silu)")
+        self.prefix, self.hidden_size, self.intermediate_size, self.activation = prefix, int(hidden_size), int(intermediate_size), activation
+        self.names = {"gate": "gate", "up": "up", "down": "down"}
+        self.names.update(names or {})
+        self.w_gate_up = self.w_down = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        p, H, I, n = self.prefix, self.hidden_size, self.intermediate_size, self.names
+        return {f"{p}.{n['gate']}": ParamSpec((I, H)), f"{p}.{n['up']}": ParamSpec((I, H)), f"{p}.{n['down']}": ParamSpec((H, I))}
+
+    def load(self, get: TensorGetter) -> None:
+        p, n = self.prefix, self.names
+        self.w_gate_up = torch.cat([get(f"{p}.{n['gate']}", "matrix"), get(f"{p}.{n['up']}", "matrix")], dim=0).contiguous()
+        self.w_down = get(f"{p}.{n['down']}", "matrix").contiguous()
+
+    def forward(self, x, ctx):
+        gate_up = linear(x, self.w_gate_up, out_dtype=torch.float32)
+        act = torch.empty((x.shape[0], self.intermediate_size), dtype=x.dtype, device=x.device)
+        kernels.gated_act(gate_up, act, self.activation)
+        return linear(act, self.w_down, out_dtype=torch.float32), None

@@ -110,3 +110,47 @@ class LayerNorm(Norm):
         if rows is None:
             stream.clear_addends()
         return out
+
+
+@register_norm("rms_norm_multi")
+class RMSNormMulti(Norm):
+    """Several RMS norms of the same rows that differ in their weights only (the sublayers of a layer that run side by
+    side, each behind a norm of its own): ``x / sqrt(mean(x^2) + eps) * w_j`` for every name in ``names``, from one pass
+    over the row. The kernel first adds what is pending on the stream into the float32 residual: one addend (with its
+    bias) or the two of sublayers that ran side by side. ``add_norm`` gives the first weight's rows in the compute type
+    (so the part also serves as a plain norm, with ``rows`` for a model's last norm); ``add_norm_all`` gives all of them
+    side by side as float32 ``[tokens, k size]`` for a reader that goes on in 32-bit."""
+
+    graph_safe = True
+
+    def __init__(self, prefix: str, size: int, eps: float, names):
+        self.prefix, self.size, self.eps = prefix, int(size), float(eps)
+        self.names = tuple(names)
+        if not self.names:
+            raise ValueError("a norm needs at least one weight")
+        self.weights: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {name: ParamSpec((self.size,), role="vector", init="norm") for name in self.names}
+
+    def load(self, get: TensorGetter) -> None:
+        self.weights = torch.stack([get(name, "vector").float() for name in self.names]).contiguous()
+
+    def _run(self, stream: ResidualStream, weights: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor]) -> torch.Tensor:
+        if not stream.plain:
+            stream.fold()                               # a normed addend or a mix over depth: the general kernel first
+        first, second = stream.take_addends()
+        kernels.add_rmsnorm_multi(stream.residual, first, second, stream.pending_bias if first is not None else None, weights,
+                                  self.eps, out, rows=rows)
+        if rows is None:
+            stream.clear_addends()
+        return out
+
+    def add_norm(self, stream: ResidualStream, ctx, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        count = rows.numel() if rows is not None else stream.residual.shape[0]
+        out = torch.empty((count, self.size), dtype=ctx.dtype, device=stream.residual.device)
+        return self._run(stream, self.weights[:1], out, rows)
+
+    def add_norm_all(self, stream: ResidualStream, ctx) -> torch.Tensor:
+        out = torch.empty((stream.residual.shape[0], len(self.names) * self.size), dtype=torch.float32, device=stream.residual.device)
+        return self._run(stream, self.weights, out, None)

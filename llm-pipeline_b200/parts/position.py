@@ -10,7 +10,13 @@ src/llm_pipeline/models/qwen3/custom_builder.py:269-288: ``inv_freq[j] = 1 / the
 ``frequency_scaling`` (optional: ``factor``, ``low``, ``high``, ``original``) rescales the frequencies by wavelength
 before any angle is taken: with wavelength l = 2 pi / f, f stays where l < original / high, becomes f / factor where
 l > original / low, and between the two is the blend (1 - s) f / factor + s f with s = (original / l - low) / (high - low).
-The frequencies are computed in float64 on the host and stored as float32; angles are float32 products."""
+The frequencies are computed in float64 on the host and stored as float32; angles are float32 products.
+
+A rule with ``"kind": "ramp"`` (``factor``, ``original``, ``fast``, ``slow``) blends by the entry's index instead: with
+``where(t) = dims * ln(original / (2 pi t)) / (2 ln theta)`` (the index whose wave makes t turns over the original length),
+lo = max(floor(where(fast)), 0), hi = min(ceil(where(slow)), dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1),
+the frequency is ``f_i / factor * ramp_i + f_i * (1 - ramp_i)``. A design that also scales cos and sin (by
+``0.1 ln(factor) + 1``, say) passes that number as ``scaling``."""
 
 from __future__ import annotations
 
@@ -38,8 +44,8 @@ class RotaryPositions(PositionEncoding):
             exponent = torch.arange(0, self.rotary_dim, 2, dtype=torch.int64).float() / self.rotary_dim
             self._inv_freq_cpu = 1.0 / (self.theta ** exponent)
         else:
-            self._inv_freq_cpu = torch.tensor(self.rescaled_frequencies(self.rotary_dim, self.theta, self.frequency_scaling),
-                                              dtype=torch.float64).float()
+            rule = self.ramp_frequencies if self.frequency_scaling.get("kind") == "ramp" else self.rescaled_frequencies
+            self._inv_freq_cpu = torch.tensor(rule(self.rotary_dim, self.theta, self.frequency_scaling), dtype=torch.float64).float()
         self._inv_freq = None
 
     @staticmethod
@@ -58,6 +64,24 @@ class RotaryPositions(PositionEncoding):
             else:
                 s = (original / wave - low) / (high - low)
                 out.append((1.0 - s) * f / factor + s * f)
+        return out
+
+    @staticmethod
+    def ramp_frequencies(rotary_dim: int, theta: float, rule: Dict[str, float]):
+        factor, original, fast, slow = (float(rule[k]) for k in ("factor", "original", "fast", "slow"))
+        if not (factor > 0 and original > 0 and fast > 0 and slow > 0 and theta > 1):
+            raise ValueError(f"a frequency ramp needs positive factor, original, fast and slow, got {rule}")
+
+        def where(turns: float) -> float:
+            return rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+        lo = max(math.floor(where(fast)), 0)
+        hi = min(math.ceil(where(slow)), rotary_dim - 1)
+        out = []
+        for i in range(rotary_dim // 2):
+            f = theta ** (-2.0 * i / rotary_dim)
+            ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            out.append(f / factor * ramp + f * (1.0 - ramp))
         return out
 
     def tables(self, ctx):
