@@ -190,16 +190,17 @@ class TupidraConfig(ModelConfig):
                     "rot_dims": rot_dims, "q_rank": int(m["q_rank"]), "sink": True, "gate": True, "own_rows": pages_from is None,
                     "interleaved": True}, f"{p}.mix")
             names = [f"{p}.norm1"] + ([f"{p}.norm2"] if mlp is not None else [])
+            spare = [] if mlp is not None else [f"{p}.norm2"]            # a checkpoint may hold them for a layer without a feed-forward
             feed_forward = None
             if mlp is not None:
                 feed_forward = PartSpec("gated_mlp", {"hidden_size": D, "intermediate_size": int(mlp["ff"]), "activation": "gelu_tanh"},
                                         f"{p}.mlp")
             block_args: Dict[str, Any] = {}
             if self.canon_taps > 0:
-                block_args["input_conv"] = {"taps": self.canon_taps,
+                block_args["input_conv"] = {"taps": self.canon_taps, "unused": [] if mlp is not None else [f"{p}.canon2"],
                                             "names": [f"{p}.canon1"] + ([f"{p}.canon2"] if mlp is not None else [])}
             layers.append(LayerSpec(block="parallel_residual", mixer=mixer, feed_forward=feed_forward,
-                                    norms={"mixer": PartSpec("rms_norm_multi", {"size": D, "eps": self.norm_eps, "names": names})},
+                                    norms={"mixer": PartSpec("rms_norm_multi", {"size": D, "eps": self.norm_eps, "names": names, "unused": spare})},
                                     block_args=block_args))
             schedule.append(ScheduleEntry(i, i, pages_from))
         spec = ModelSpec(

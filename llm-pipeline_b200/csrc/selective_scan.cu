@@ -36,8 +36,10 @@ struct ScanArgs {
 };
 
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+__device__ __forceinline__ float ss_exp(float v) { return expf(v); }
+__device__ __forceinline__ double ss_exp(double v) { return exp(v); }
 
-template <typename T, int NS>
+template <typename T, typename ACC, int NS>
 __global__ void __launch_bounds__(SS_THREADS) selective_scan_kernel(const ScanArgs a) {
     extern __shared__ float bc_s[];                            // [SS_CHUNK][2 states]
     const int r = blockIdx.x;
@@ -52,12 +54,13 @@ __global__ void __launch_bounds__(SS_THREADS) selective_scan_kernel(const ScanAr
     float* slot = a.state + (size_t)a.slots[r] * a.state_slot;
     const float* rd = slot + ((p0 + 1) & 1) * a.state_half;
     float* wr = slot + ((p0 + end - begin - 1) & 1) * a.state_half;
-    float S[NS], A[NS];
+    ACC S[NS];
+    float A[NS];
 #pragma unroll
     for (int k = 0; k < NS; ++k) {
         const int n = k * L + l;
         const bool have = ok && n < Nst;
-        S[k] = have ? rd[(size_t)c * Nst + n] : 0.f;
+        S[k] = have ? (ACC)rd[(size_t)c * Nst + n] : (ACC)0;
         A[k] = have ? a.A[(size_t)c * Nst + n] : 0.f;
     }
     const float dt_b = ok ? a.dt_bias[c] : 0.f;
@@ -84,23 +87,24 @@ __global__ void __launch_bounds__(SS_THREADS) selective_scan_kernel(const ScanAr
 #pragma unroll
         for (int tt = 0; tt < SS_CHUNK; ++tt) {
             if (tt < nt) {
-                const float dtv = dr[tt], dx = dtv * xr[tt];
+                const ACC dtv = dr[tt], dx = dtv * (ACC)xr[tt];
                 const float* Bs = bc_s + tt * 2 * Nst;
                 const float* Cs = Bs + Nst;
-                float y = 0.f;
+                ACC y = 0;
 #pragma unroll
                 for (int k = 0; k < NS; ++k) {
                     const int n = k * L + l;
                     if (n < Nst) {
-                        S[k] = fmaf(expf(dtv * A[k]), S[k], dx * Bs[n]);
-                        y = fmaf(S[k], Cs[n], y);
+                        S[k] = fma(ss_exp(dtv * (ACC)A[k]), S[k], dx * (ACC)Bs[n]);
+                        y = fma(S[k], (ACC)Cs[n], y);
                     }
                 }
                 for (int o = L >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
                 if (ok && l == 0) {
-                    y = fmaf(Dc, xr[tt], y);
-                    if (a.z) y *= zr[tt] / (1.f + expf(-zr[tt]));
-                    out[(size_t)(t0 + tt) * a.out_t + c] = from_float<T>(y);
+                    y = fma((ACC)Dc, (ACC)xr[tt], y);
+                    float yf = (float)y;
+                    if (a.z) yf *= zr[tt] / (1.f + expf(-zr[tt]));
+                    out[(size_t)(t0 + tt) * a.out_t + c] = from_float<T>(yf);
                 }
             }
         }
@@ -108,7 +112,7 @@ __global__ void __launch_bounds__(SS_THREADS) selective_scan_kernel(const ScanAr
 #pragma unroll
     for (int k = 0; k < NS; ++k) {
         const int n = k * L + l;
-        if (ok && n < Nst) wr[(size_t)c * Nst + n] = S[k];
+        if (ok && n < Nst) wr[(size_t)c * Nst + n] = (float)S[k];
     }
 }
 
@@ -135,11 +139,11 @@ LLMP_API int llmp_selective_scan(const float* x, long x_t, const float* dt, long
     dim3 grid(R, (unsigned)blocks_y);
     const size_t smem = (size_t)SS_CHUNK * 2 * states * sizeof(float);
     if (out_dtype == LLMP_BF16) {
-        if (NS == 4) selective_scan_kernel<bf16, 4><<<grid, SS_THREADS, smem, stream>>>(a);
-        else selective_scan_kernel<bf16, 8><<<grid, SS_THREADS, smem, stream>>>(a);
+        if (NS == 4) selective_scan_kernel<bf16, float, 4><<<grid, SS_THREADS, smem, stream>>>(a);
+        else selective_scan_kernel<bf16, float, 8><<<grid, SS_THREADS, smem, stream>>>(a);
     } else {
-        if (NS == 4) selective_scan_kernel<float, 4><<<grid, SS_THREADS, smem, stream>>>(a);
-        else selective_scan_kernel<float, 8><<<grid, SS_THREADS, smem, stream>>>(a);
+        if (NS == 4) selective_scan_kernel<float, double, 4><<<grid, SS_THREADS, smem, stream>>>(a);
+        else selective_scan_kernel<float, double, 8><<<grid, SS_THREADS, smem, stream>>>(a);
     }
     return llmp_check_launch("selective_scan");
 }

@@ -87,7 +87,7 @@ class ParallelResidualBlock(Block):
             names = list(input_conv["names"])
             if len(names) != self.sublayers:
                 raise ValueError(f"a layer of {self.sublayers} sublayers needs as many input convolutions, got {names}")
-            self.input_conv = InputConv(norm.size, int(input_conv["taps"]), names)
+            self.input_conv = InputConv(norm.size, int(input_conv["taps"]), names, input_conv.get("unused", ()))
         if hasattr(norm, "add_norm_all") and len(norm.names) != self.sublayers:
             raise ValueError(f"a layer of {self.sublayers} sublayers needs as many norm weights, got {list(norm.names)}")
         self._own_state = self.input_conv.state_entries() if self.input_conv is not None else 0
@@ -112,9 +112,7 @@ class ParallelResidualBlock(Block):
             return h, h
         normed = norm.add_norm_all(stream, ctx)                       # float32 [tokens, sublayers * size]
         if self.input_conv is not None:
-            if cache.state is None:
-                raise RuntimeError("the layer's input convolution needs its state slots")
-            hs = self.input_conv.forward(normed, ctx, cache.state, 0)
+            hs = self.input_conv.forward(normed, ctx, cache.state if self._own_state else None, 0)
         else:
             hs = torch.empty((self.sublayers, normed.shape[0], norm.size), dtype=ctx.dtype, device=normed.device)
             for j in range(self.sublayers):

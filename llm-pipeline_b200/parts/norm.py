@@ -123,15 +123,18 @@ class RMSNormMulti(Norm):
 
     graph_safe = True
 
-    def __init__(self, prefix: str, size: int, eps: float, names):
+    def __init__(self, prefix: str, size: int, eps: float, names, unused=()):
+        """``unused``: names of weights a checkpoint may hold although no sublayer of this layer reads them."""
         self.prefix, self.size, self.eps = prefix, int(size), float(eps)
-        self.names = tuple(names)
+        self.names, self.unused = tuple(names), tuple(unused)
         if not self.names:
             raise ValueError("a norm needs at least one weight")
         self.weights: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {name: ParamSpec((self.size,), role="vector", init="norm") for name in self.names}
+        specs = {name: ParamSpec((self.size,), role="vector", init="norm") for name in self.names}
+        specs.update({name: ParamSpec((self.size,), role="vector", optional=True, init="norm") for name in self.unused})
+        return specs
 
     def load(self, get: TensorGetter) -> None:
         self.weights = torch.stack([get(name, "vector").float() for name in self.names]).contiguous()

@@ -83,6 +83,19 @@ def latent_rows(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict, ep
     return c, k_rot
 
 
+def attend_latent(q_plain, q_rot, k, k_rot, v, scale: float, sink: torch.Tensor) -> torch.Tensor:
+    """q_plain [T, H, dim], q_rot [T, H, rot] (rotated), k [T, H, dim], k_rot [T, rot] (rotated, shared by the heads), v [T, H,
+    vdim]; causal softmax whose denominator also holds exp(sink_h). Returns [T, H, vdim]."""
+    T = q_plain.shape[0]
+    scores = (torch.einsum("ihd,jhd->hij", q_plain, k) + torch.einsum("ihd,jd->hij", q_rot, k_rot)) * scale
+    mask = torch.tril(torch.ones(T, T, dtype=torch.bool))
+    scores = scores.masked_fill(~mask, -math.inf)
+    top = torch.maximum(scores.max(dim=-1).values, sink[:, None])
+    e = torch.exp(scores - top[..., None])
+    prob = e / (e.sum(dim=-1) + torch.exp(sink[:, None] - top))[..., None]
+    return torch.einsum("hij,jhd->ihd", prob, v)
+
+
 def latent_attention(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict, eps: float, shared=None):
     """``shared``: (c, k_rot) of the layer whose cache this one reads, or None for a layer with rows of its own.
     Returns (output, (c, k_rot))."""
@@ -90,21 +103,34 @@ def latent_attention(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dic
     rot, T = m["rot"], h.shape[0]
     cq = rms(h @ W[f"{p}.dq"].T, eps, W[f"{p}.dq.norm"])
     q = (cq @ W[f"{p}.uq"].T).view(T, H, dim + rot_dim)
-    q_plain = q[..., :dim]
     q_rot = rotate_interleaved(q[..., dim:], torch.arange(T), int(rot["dims"]), float(rot["base"]), rot.get("scaling"))
     c, k_rot = shared if shared is not None else latent_rows(h, W, p, m, eps)
     k = (c @ W[f"{p}.uk"].T).view(T, H, dim)
     v = (c @ W[f"{p}.uv"].T).view(T, H, vdim)
-    scores = (torch.einsum("ihd,jhd->hij", q_plain, k) + torch.einsum("ihd,jd->hij", q_rot, k_rot)) * float(m["scale"])
-    mask = torch.tril(torch.ones(T, T, dtype=torch.bool))
-    scores = scores.masked_fill(~mask, -math.inf)
-    sink = W[f"{p}.sink"].to(F)
-    top = torch.maximum(scores.max(dim=-1).values, sink[:, None])
-    e = torch.exp(scores - top[..., None])
-    prob = e / (e.sum(dim=-1) + torch.exp(sink[:, None] - top))[..., None]
-    heads = torch.einsum("hij,jhd->ihd", prob, v).reshape(T, H * vdim)
+    heads = attend_latent(q[..., :dim], q_rot, k, k_rot, v, float(m["scale"]), W[f"{p}.sink"].to(F)).reshape(T, H * vdim)
     heads = heads * torch.sigmoid(h @ W[f"{p}.g"].T)
     return heads @ W[f"{p}.o"].T, (c, k_rot)
+
+
+def attend_window(q, k, v, scale: float, cap, size, keep: int) -> torch.Tensor:
+    """q [T, H, dim], k [T, G, dim], v [T, G, vdim] (already normed); capped scores minus the distance bias, the window with
+    its kept first tokens, and one added to the softmax's denominator. Returns [T, H, vdim]."""
+    T, H, G = q.shape[0], q.shape[1], k.shape[1]
+    group = torch.arange(H) // (H // G)
+    s = torch.einsum("ihd,jhd->hij", q, k[:, group]) * scale
+    if cap:
+        s = float(cap) * torch.tanh(s / float(cap))
+    i, j = torch.arange(T)[:, None], torch.arange(T)[None, :]
+    slopes = torch.tensor([2.0 ** (-8.0 * (n + 1) / H) for n in range(H)], dtype=F)
+    s = s - slopes[:, None, None] * (i - j).to(F)
+    seen = j <= i
+    if size is not None:
+        seen = seen & ((i - j < int(size)) | (j < int(keep)))
+    s = s.masked_fill(~seen, -math.inf)
+    top = s.max(dim=-1).values.clamp(min=0.0)
+    e = torch.exp(s - top[..., None])
+    prob = e / (torch.exp(-top) + e.sum(dim=-1))[..., None]
+    return torch.einsum("hij,jhd->ihd", prob, v[:, group])
 
 
 def window_attention(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict, eps: float) -> torch.Tensor:
@@ -113,43 +139,31 @@ def window_attention(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dic
     q = (h @ W[f"{p}.q"].T + W[f"{p}.q.b"]).view(T, H, dim)
     k = (h @ W[f"{p}.k"].T + W[f"{p}.k.b"]).view(T, G, dim)
     v = rms((h @ W[f"{p}.v"].T + W[f"{p}.v.b"]).view(T, G, vdim), eps)
-    group = torch.arange(H) // (H // G)
-    s = torch.einsum("ihd,jhd->hij", q, k[:, group]) * float(m["scale"])
-    cap = m.get("softcap")
-    if cap:
-        s = float(cap) * torch.tanh(s / float(cap))
-    i, j = torch.arange(T)[:, None], torch.arange(T)[None, :]
-    slopes = torch.tensor([2.0 ** (-8.0 * (n + 1) / H) for n in range(H)], dtype=F)
-    s = s - slopes[:, None, None] * (i - j).to(F)
     mask = m.get("mask") or {}
-    size, keep = mask.get("size"), int(mask.get("keep_first") or 0)
-    seen = j <= i
-    if size is not None:
-        seen = seen & ((i - j < int(size)) | (j < keep))
-    s = s.masked_fill(~seen, -math.inf)
-    top = s.max(dim=-1).values.clamp(min=0.0)
-    e = torch.exp(s - top[..., None])
-    prob = e / (torch.exp(-top) + e.sum(dim=-1))[..., None]
-    heads = torch.einsum("hij,jhd->ihd", prob, v[:, group]).reshape(T, H * vdim)
-    heads = heads * torch.sigmoid(h @ W[f"{p}.g"].T)
+    heads = attend_window(q, k, v, float(m["scale"]), m.get("softcap"), mask.get("size"), int(mask.get("keep_first") or 0))
+    heads = heads.reshape(T, H * vdim) * torch.sigmoid(h @ W[f"{p}.g"].T)
     return heads @ W[f"{p}.o"].T + W[f"{p}.o.b"]
+
+
+def scan(x, dt, A, B, C, D, S=None):
+    """The recurrence itself on given rows: x, dt [T, inner], A [inner, N], B, C [T, N]; returns (y [T, inner], last state)."""
+    T, inner = x.shape
+    S = torch.zeros(inner, A.shape[1], dtype=F) if S is None else S
+    y = torch.zeros(T, inner, dtype=F)
+    for t in range(T):
+        S = torch.exp(dt[t][:, None] * A) * S + (dt[t] * x[t])[:, None] * B[t][None, :]
+        y[t] = S @ C[t] + D * x[t]
+    return y, S
 
 
 def selective_scan(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict) -> torch.Tensor:
     inner, N, R = int(m["inner"]), int(m["state"]), int(m["dt_rank"])
-    T = h.shape[0]
     xz = h @ W[f"{p}.in"].T
     x, z = xz[:, :inner], xz[:, inner:]
     x = silu(causal_conv(x, W[f"{p}.conv"], W[f"{p}.conv.b"]))
     dbc = x @ W[f"{p}.x"].T
     dt = torch.nn.functional.softplus(dbc[:, :R] @ W[f"{p}.dt"].T + W[f"{p}.dt.b"])
-    B, C = dbc[:, R:R + N], dbc[:, R + N:R + 2 * N]
-    A = -torch.exp(W[f"{p}.A_log"])
-    S = torch.zeros(inner, N, dtype=F)
-    y = torch.zeros(T, inner, dtype=F)
-    for t in range(T):
-        S = torch.exp(dt[t][:, None] * A) * S + (dt[t] * x[t])[:, None] * B[t][None, :]
-        y[t] = S @ C[t] + W[f"{p}.D"] * x[t]
+    y, _ = scan(x, dt, -torch.exp(W[f"{p}.A_log"]), dbc[:, R:R + N], dbc[:, R + N:R + 2 * N], W[f"{p}.D"])
     return (y * silu(z)) @ W[f"{p}.o"].T
 
 
@@ -161,12 +175,14 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: List[int], r
     """Logits [T, vocab] of one sequence (and, on request, the residual after every layer, [layers, T, width])."""
     W = {k: (v.to(F) if v.is_floating_point() else v) for k, v in weights.items()}
     eps = float(config["norm"]["eps"])
+    taps = int((config.get("canon") or {}).get("taps") or 0)
+    filtered = (lambda h, name: input_conv(h, W[name])) if taps else (lambda h, name: h)
     x = W["embed"][torch.tensor(tokens, dtype=torch.long)]
     kept = {}
     after = []
     for i, layer in enumerate(config["layers"]):
         p, m = f"l{i}", layer["mixer"]
-        h = input_conv(rms(x, eps, W[f"{p}.norm1"]), W[f"{p}.canon1"])
+        h = filtered(rms(x, eps, W[f"{p}.norm1"]), f"{p}.canon1")
         if layer["type"] == "mamba1":
             out = selective_scan(h, W, f"{p}.mix", m)
         elif layer["type"] == "attention":
@@ -177,8 +193,41 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: List[int], r
         else:
             raise ValueError(layer["type"])
         if layer.get("mlp") is not None:
-            out = out + dense_ff(input_conv(rms(x, eps, W[f"{p}.norm2"]), W[f"{p}.canon2"]), W, f"{p}.mlp")
+            out = out + dense_ff(filtered(rms(x, eps, W[f"{p}.norm2"]), f"{p}.canon2"), W, f"{p}.mlp")
         x = x + out
         after.append(x)
     logits = rms(x, eps, W["final.norm"]) @ W["head"].T
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+def expected_tensors(config: dict) -> Dict[str, tuple]:
+    """Every tensor a model of this configuration has, with its shape."""
+    D, V = int(config["width"]), int(config["vocab"])
+    taps = int((config.get("canon") or {}).get("taps") or 0)
+    out = {"embed": (V, D), "final.norm": (D,), "head": (V, D)}
+    for i, layer in enumerate(config["layers"]):
+        p, m = f"l{i}", layer["mixer"]
+        out[f"{p}.norm1"] = (D,)
+        if taps:
+            out[f"{p}.canon1"] = (D, taps)
+        if layer.get("mlp") is not None:
+            ff = int(layer["mlp"]["ff"])
+            out.update({f"{p}.norm2": (D,), f"{p}.mlp.gate": (ff, D), f"{p}.mlp.up": (ff, D), f"{p}.mlp.down": (D, ff)})
+            if taps:
+                out[f"{p}.canon2"] = (D, taps)
+        x = f"{p}.mix"
+        if layer["type"] == "mamba1":
+            I, N, R, K = (int(m[k]) for k in ("inner", "state", "dt_rank", "conv"))
+            out.update({f"{x}.in": (2 * I, D), f"{x}.conv": (I, K), f"{x}.conv.b": (I,), f"{x}.x": (R + 2 * N, I), f"{x}.dt": (I, R),
+                        f"{x}.dt.b": (I,), f"{x}.A_log": (I, N), f"{x}.D": (I,), f"{x}.o": (D, I)})
+        elif layer["type"] == "attention":
+            H, G, d, dv = (int(m[k]) for k in ("heads", "kv_heads", "dim", "vdim"))
+            out.update({f"{x}.q": (H * d, D), f"{x}.q.b": (H * d,), f"{x}.k": (G * d, D), f"{x}.k.b": (G * d,), f"{x}.v": (G * dv, D),
+                        f"{x}.v.b": (G * dv,), f"{x}.g": (H * dv, D), f"{x}.o": (D, H * dv), f"{x}.o.b": (D,)})
+        else:
+            H, d, r, dv, rank, qr = (int(m[k]) for k in ("heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank"))
+            out.update({f"{x}.dq": (qr, D), f"{x}.dq.norm": (qr,), f"{x}.uq": (H * (d + r), qr), f"{x}.uk": (H * d, rank),
+                        f"{x}.uv": (H * dv, rank), f"{x}.sink": (H,), f"{x}.g": (H * dv, D), f"{x}.o": (D, H * dv)})
+            if m.get("kv_from") is None:
+                out.update({f"{x}.dkv": (rank + r, D), f"{x}.dkv.norm": (rank,)})
+    return out
