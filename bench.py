@@ -30,6 +30,9 @@ time of every kernel class of both, in one JSON line of its own shape.
 ``--compare razelorn [--size 1k|2k]`` does the same for the Razelorn decoder (differential attention under a sliding
 window beside a dense or routed-expert feed-forward on one layer norm).
 
+``--compare tupidra [--size 1k|2k]`` does the same for the Tupidra decoder (a selective scan, capped window attention with
+kept first tokens, latent attention with query latents, sinks, gates and shared rows, each beside a gated GELU
+feed-forward behind norms and input filters of its own).
 ``--compare nufolix [--size 1k|2k]`` does the same for the Nufolix decoder (a state-space mixer; sigmoid attention with
 mixed heads side by side with a gated delta rule; dense xIELU feed-forwards).
 
@@ -859,11 +862,70 @@ def nufolix_work(z, tokens, keys_per_token, decode, requests=1):
     return work
 
 
+# ``--compare tupidra``: the same two measurements for the Tupidra decoder: four layers (a selective scan; capped window
+# attention with kept first tokens; latent attention with query latents, sinks and gates; a latent attention layer that
+# reads the third layer's rows), each beside a gated GELU feed-forward behind norms and input filters of its own, beside a
+# Qwen3 dense decoder of the same width, depth and vocabulary.
+TUPIDRA_SIZES = {
+    "1k": {"width": 1024, "inner": 2048, "state": 16, "dt_rank": 64, "conv": 4, "taps": 4, "heads": 8, "kv_heads": 4, "dim": 128,
+           "vdim": 128, "window": 1024, "keep": 4, "lat_heads": 8, "lat_dim": 64, "rot": 32, "lat_vdim": 64, "rank": 256, "q_rank": 384,
+           "ff": 4096, "layers": 4, "vocab": 32000, "qwen_heads": (8, 4)},
+    "2k": {"width": 2048, "inner": 4096, "state": 16, "dt_rank": 128, "conv": 4, "taps": 4, "heads": 16, "kv_heads": 4, "dim": 128,
+           "vdim": 128, "window": 1024, "keep": 4, "lat_heads": 16, "lat_dim": 128, "rot": 64, "lat_vdim": 128, "rank": 512, "q_rank": 768,
+           "ff": 8192, "layers": 4, "vocab": 32000, "qwen_heads": (16, 8)},
+}
+
+
+def tupidra_config(z):
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    latent = {"heads": z["lat_heads"], "dim": z["lat_dim"], "rot_dim": z["rot"], "vdim": z["lat_vdim"], "kv_rank": z["rank"],
+              "q_rank": z["q_rank"], "scale": (z["lat_dim"] + z["rot"]) ** -0.5,
+              "rot": {"base": 500000.0, "dims": z["rot"], "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    kinds = [{"type": "mamba1", "mixer": {"inner": z["inner"], "state": z["state"], "dt_rank": z["dt_rank"], "conv": z["conv"]}, "mlp": mlp},
+             {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"],
+                                             "scale": z["dim"] ** -0.5, "softcap": 30.0, "mask": {"size": z["window"], "keep_first": z["keep"]}},
+              "mlp": mlp},
+             {"type": "latent_attention", "mixer": latent, "mlp": mlp},
+             {"type": "latent_attention", "mixer": {**latent, "kv_from": 2}, "mlp": mlp}]
+    layers = [kinds[i % 4] if i % 4 != 3 else {**kinds[3], "mixer": {**latent, "kv_from": i - 1}} for i in range(z["layers"])]
+    return {"architecture": "Tupidra", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "canon": {"taps": z["taps"]},
+            "layers": layers}
+
+
+def tupidra_work(z, tokens, keys_per_token, decode, requests=1):
+    """Closed-form work of the design's own kernel classes for one step: label -> (bytes, flops)."""
+    D, L = z["width"], z["layers"]
+    scan_layers, win_layers, lat_layers = (L + 3) // 4, (L + 2) // 4, (L + 1) // 4 + L // 4
+    I, N, R = z["inner"], z["state"], z["dt_rank"]
+    H, G, d, dv = z["heads"], z["kv_heads"], z["dim"], z["vdim"]
+    dk = z["rank"] + z["rot"]
+    work = {}
+    # residual and two addends in and out in float32, two normed rows out in float32; the last norm reads a few rows only
+    work["add_rmsnorm_multi"] = (L * tokens * D * (4 + 4 + 4 + 4 + 8), 0.0)
+    # the layers' input filters (two float32 inputs in, two typed rows out) and the scan's own convolution (float32 in, float32 and typed out)
+    work["short_conv"] = (L * tokens * 2 * D * (4 + 2) + scan_layers * tokens * I * (4 + 4 + 2), 0.0)
+    work["selective_scan"] = (scan_layers * (tokens * (3 * I * 4 + 2 * N * 4 + I * 2) + requests * I * N * 8), 0.0)
+    work["gated_act"] = (L * tokens * z["ff"] * (8 + 2), 0.0)
+    work["capped_qkv_post"] = (win_layers * tokens * ((H + G) * d + G * dv) * (4 + 2), 0.0)
+    work["latent_rows_post"] = (lat_layers * tokens * (z["lat_heads"] * (z["lat_dim"] + z["rot"]) + dk) * (4 + 2), 0.0)
+    work["sigmoid_gate"] = (lat_layers * tokens * z["lat_heads"] * z["lat_vdim"] * (2 + 4 + 2), 0.0)
+    seen = min(keys_per_token, z["window"] + z["keep"])
+    if decode:
+        work["capped_attention"] = (win_layers * tokens * seen * G * (d + dv) * 2, 0.0)
+        work["latent_attention_mma"] = (lat_layers * tokens * keys_per_token * dk * 2, 0.0)
+    else:
+        work["capped_attention"] = (0.0, win_layers * 2.0 * tokens * seen * H * (d + dv))
+        work["latent_attention_mma"] = (0.0, lat_layers * 2.0 * tokens * keys_per_token * z["lat_heads"] * (dk + z["rank"]))
+    work["capped_attention_mma"] = work["capped_attention"]
+    return work
+
+
 def run_compare(args):
     peak = peaks()
     sizes, config_of, work_of = {"zupilorn": (ZUPILORN_SIZES, zupilorn_config, zupilorn_work),
                                  "razelorn": (RAZELORN_SIZES, razelorn_config, razelorn_work),
-                                 "nufolix": (NUFOLIX_SIZES, nufolix_config, lambda z, n, k, d: nufolix_work(z, n, k, d, args.batch if d else 1))}[args.compare]
+                                 "nufolix": (NUFOLIX_SIZES, nufolix_config, lambda z, n, k, d: nufolix_work(z, n, k, d, args.batch if d else 1)),
+                                 "tupidra": (TUPIDRA_SIZES, tupidra_config, lambda z, n, k, d: tupidra_work(z, n, k, d, args.batch if d else 1))}[args.compare]
     z = sizes[args.size]
     clocks = ClockSampler()
     clocks.start()
@@ -959,7 +1021,7 @@ def main() -> int:
     parser.add_argument("--lean", action="store_true", help="leave out the per-kernel breakdown, the page-size point, the plain "
                         "PyTorch baseline and the self-check")
     parser.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per page of the key/value cache")
-    parser.add_argument("--compare", default="", choices=("", "zupilorn", "razelorn", "nufolix"),
+    parser.add_argument("--compare", default="", choices=("", "zupilorn", "razelorn", "nufolix", "tupidra"),
                         help="instead of the headline: prefill and decode of this design at real layer sizes beside a Qwen3 dense "
                         "decoder of the same width and depth, with the time of every kernel class")
     parser.add_argument("--size", default="2k", choices=tuple(ZUPILORN_SIZES), help="with --compare: the layer sizes")

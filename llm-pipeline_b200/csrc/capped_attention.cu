@@ -17,12 +17,7 @@
 // warp per query head. Keys are walked in tiles of 32 aligned to key 0; tiles that hold no key the token sees are
 // skipped, and rows of keys it does not see are never read (their pages may be gone). A row's operations depend on its
 // position alone, not on the step.
-//
-// capped_attention_mma (bfloat16, d and dv multiples of 16 up to 128): tensor-core tiles of 16 rows (new tokens of a
-// request x heads of a group), see below.
 #include "common.cuh"
-
-#include <mma.h>
 
 namespace {
 

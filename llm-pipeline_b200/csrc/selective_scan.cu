@@ -4,7 +4,10 @@
 //   dt_c = softplus(dt_raw_c + dt_bias_c)
 //   S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n          (A < 0 comes from the caller; S is zero before the first token)
 //   y_c = sum_n S[c, n] C_n + D_c x_c;      out_c = y_c * silu(z_c)   (without z: y_c)
-// x (after its convolution and activation), dt_raw, B, C and z are float32 rows of the step; everything here is float32;
+// x (after its convolution and activation), dt_raw, B, C and z are float32 rows of the step; everything here is float32
+// where the output is bfloat16. Where the output is float32 (the engine's true 32-bit path) the decays, the state and the
+// read-out of a step are float64 between the float32 state a step reads and the one it leaves: a float32 recurrence over a
+// thousand tokens with decays near one drifts by tens of units in the last place, which this keeps out of the sharper path.
 // out has the compute type. Between steps a request keeps S in its state slot, as two copies [inner][states] that take
 // turns by the parity of the last position written, so a step of one token never overwrites what it read.
 //

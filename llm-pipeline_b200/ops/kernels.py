@@ -70,6 +70,7 @@ _SIGNATURES = {
     "llmp_latent_rows_post": [_P, _L, _P, _L, _I, _I, _I, _I, _P, _I, _F, _P, _P, _I, _I, _P, _I, _L, _P, _P, _I, _P],
     "llmp_capped_qkv_post": [_P, _L, _P, _I, _F, _I, _P, _I, _L, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "llmp_capped_attention": [_P, _L, _P, _I, _P, _I, _P, _P, _P, _P, _P, _L, _P, _L, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P],
+    "llmp_capped_attention_mma": [_P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _L, _I, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P],
     "llmp_selective_scan": [_P, _L, _P, _L, _P, _P, _P, _L, _P, _P, _P, _L, _P, _L, _L, _P, _P, _P, _P, _I, _L, _I, _I, _I, _P],
     "llmp_add_rmsnorm_multi": [_P, _P, _I, _P, _I, _P, _I, _P, _I, _I, _F, _P, _I, _L, _L, _P, _I, _I, _P],
     "llmp_gated_act": [_P, _I, _L, _P, _I, _L, _I, _I, _P],
@@ -1496,6 +1497,49 @@ def capped_attention(q: torch.Tensor, pages: torch.Tensor, tables: torch.Tensor,
           _ptr(token_request), _ptr(positions), _ptr(slopes), _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0,
           _ptr(out), out.stride(0), N, num_heads, num_kv_heads, dim, vdim, pages.shape[2], int(window), int(keep_first),
           float(scale), float(softcap), _stream())
+    return out
+
+
+def capped_mma_supports(dtype: torch.dtype, dim: int, vdim: int) -> bool:
+    """Whether the tensor-core capped attention kernel serves these sizes (bfloat16)."""
+    if dtype != torch.bfloat16:
+        return False
+    fn = library().llmp_capped_mma_supports
+    fn.argtypes = [_I, _I]
+    fn.restype = _I
+    return bool(fn(dim, vdim))
+
+
+def capped_mma_tokens_per_tile(num_heads: int, num_kv_heads: int) -> int:
+    fn = library().llmp_capped_mma_tokens_per_tile
+    fn.argtypes = [_I, _I]
+    fn.restype = _I
+    return int(fn(num_heads, num_kv_heads))
+
+
+def capped_attention_mma(q: torch.Tensor, pages: torch.Tensor, tables: torch.Tensor, q_start: torch.Tensor, ctx_len: torch.Tensor,
+                         tile_req: torch.Tensor, tile_tok0: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int, dim: int,
+                         vdim: int, window: int, keep_first: int, scale: float, softcap: float, slopes: Optional[torch.Tensor] = None,
+                         sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, split: bool = False) -> torch.Tensor:
+    """``capped_attention`` on the tensor cores for bfloat16 (csrc/capped_attention_mma.cu). ``tile_req``/``tile_tok0``: the work
+    list (request and first token of every tile of ``capped_mma_tokens_per_tile`` tokens). ``split``: every tile is one token,
+    and the four warps of a block share its keys."""
+    N = q.shape[0]
+    _need(q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16 and out.dtype == torch.bfloat16, "capped_attention_mma takes bfloat16")
+    _need(q.stride(1) == 1 and q.shape[1] == num_heads * dim and out.shape == (N, num_heads * vdim) and out.stride(1) == 1,
+          "capped attention shapes do not match")
+    _need(pages.is_contiguous() and pages.dim() == 4 and pages.shape[1] == num_kv_heads and pages.shape[3] == dim + vdim,
+          "capped attention pages have the wrong layout")
+    _sink(sink, num_heads); _sink(slopes, num_heads)
+    _need(gate is None or (gate.dtype == torch.float32 and gate.shape == (N, num_heads * vdim) and gate.stride(1) == 1),
+          "the gate must be float32 [tokens, heads vdim]")
+    for t, name in ((tables, "tables"), (q_start, "q_start"), (ctx_len, "ctx_len"), (tile_req, "tile_req"), (tile_tok0, "tile_tok0")):
+        _i32(t, name)
+    _need(not split or tile_req.numel() == N, "warps share a tile's keys only in steps of one token a request")
+    _call("llmp_capped_attention_mma", _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(pages), _ptr(tables), tables.shape[1],
+          _ptr(q_start), _ptr(ctx_len), _ptr(tile_req), _ptr(tile_tok0), tile_req.numel(), _ptr(slopes), _ptr(sink), _ptr(gate),
+          gate.stride(0) if gate is not None else 0, num_heads, num_kv_heads, dim, vdim, pages.shape[2], int(window), int(keep_first),
+          float(scale), float(softcap), 1 if split else 0, _stream())
     return out
 
 

@@ -17,7 +17,9 @@ No rotation: positions enter through the distance bias and the mask alone; kept 
 The projections that read h are one product against [Wq; Wk; Wv; Wg] with a float32 result; one kernel adds the biases,
 norms the values, writes the queries in the compute type and the token's [k | v] rows into its page slot; the attention
 kernel reads all keys and values from pages, this step's included, and applies the gate as it stores. Scores, cap, bias,
-softmax and weighted sums are float32 (``csrc/capped_attention.cu``). The pages of a windowed layer go back to the pool
+softmax and weighted sums are float32 (``csrc/capped_attention.cu``: any sizes, both types; ``csrc/capped_attention_mma.cu``:
+bfloat16 on the tensor cores for key and value sizes of 16, 32, 64 and 128, the probabilities rounded to bfloat16 for the
+product with the values). The pages of a windowed layer go back to the pool
 as the window passes them, but for those of the kept tokens (``HeadRowPagesSpec(window, keep_first)``)."""
 
 from __future__ import annotations
@@ -30,6 +32,7 @@ from ..cache.spec import HeadRowPagesSpec
 from ..ops import kernels
 from ..ops.linear import linear
 from ..weights.source import ParamSpec
+from .attention import AttentionPolicy
 from .base import LayerCache, Mixer, TensorGetter
 from .registry import register_mixer
 
@@ -73,6 +76,22 @@ class CappedAttention(Mixer):
     def _name(self, key: str) -> str:
         return f"{self.prefix}.{self.names[key]}"
 
+    def _tiles(self, ctx, per_tile: int):
+        key = ("capped_attention_tiles", per_tile)
+        tiles = ctx.memo.get(key)
+        if tiles is None:
+            if ctx.max_q_len == 1:
+                # one token a request: tile r is request r (made on the device, so that a captured step holds no copy from the host)
+                tiles = (torch.arange(ctx.num_requests, dtype=torch.int32, device=ctx.device),
+                         torch.zeros(ctx.num_requests, dtype=torch.int32, device=ctx.device))
+            else:
+                req, tok0, _seg, _slot, _places = AttentionPolicy.plan_items(ctx.starts, ctx.q_lens, per_tile, 0, 1, 1, kernels.sm_count())
+                host = torch.tensor([req, tok0], dtype=torch.int32).pin_memory()
+                dev = host.to(ctx.device, non_blocking=True)
+                tiles = (dev[0].contiguous(), dev[1].contiguous())
+            ctx.memo[key] = tiles
+        return tiles
+
     def param_specs(self) -> Dict[str, ParamSpec]:
         D = self.hidden_size
         sizes = {"q": self.q_size, "k": self.k_size, "v": self.v_size}
@@ -115,6 +134,15 @@ class CappedAttention(Mixer):
         kernels.capped_qkv_post(proj[:, :width], self.b_qkv, self.value_norm_eps, q, ctx.slot_mapping[cache.group] if cache.writes else None,
                                 cache.pages if cache.writes else None, self.num_heads, self.num_kv_heads, self.dim, self.vdim)
         out = torch.empty((N, self.o_size), dtype=x.dtype, device=x.device)
+        gate = proj[:, width:] if self.gate else None
+        if kernels.capped_mma_supports(x.dtype, self.dim, self.vdim) and (width % 2 == 0 or not self.gate):
+            # bfloat16 and sizes the tensor-core kernel has instances of: prompts in tiles of 64 rows (token, head of a group),
+            # single tokens with the four warps of a block sharing the keys
+            tile_req, tile_tok0 = self._tiles(ctx, kernels.capped_mma_tokens_per_tile(self.num_heads, self.num_kv_heads))
+            kernels.capped_attention_mma(q, cache.pages, ctx.block_tables[cache.group], ctx.q_start, ctx.ctx_len, tile_req, tile_tok0, out,
+                                         self.num_heads, self.num_kv_heads, self.dim, self.vdim, self.window or 0, self.keep_first,
+                                         self.scale, self.softcap, slopes=self.slopes, sink=self.sinks, gate=gate, split=ctx.max_q_len == 1)
+            return linear(out, self.w_o, out_dtype=torch.float32), self.b_o
         kernels.capped_attention(q, cache.pages, ctx.block_tables[cache.group], ctx.token_request, ctx.positions, out, self.num_heads,
                                  self.num_kv_heads, self.dim, self.vdim, self.window or 0, self.keep_first, self.scale, self.softcap,
                                  slopes=self.slopes, sink=self.sinks, gate=proj[:, width:] if self.gate else None)

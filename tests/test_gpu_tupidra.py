@@ -155,21 +155,35 @@ def _window_case(dtype, heads, kv_heads, dim, vdim, n, page, seed, cap, size, ke
     slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / heads) for h in range(heads)], dtype=torch.float32, device=DEV)
     sink = torch.zeros(heads, device=DEV)
     qd, pd = q.reshape(n, -1).to(DEV).to(dtype)[rows].contiguous(), pages.to(DEV).to(dtype)
+    gd = g.to(DEV)[rows].contiguous() if gate else None
     out = torch.empty(len(rows), heads * vdim, device=DEV, dtype=dtype)
     kernels.capped_attention(qd, pd, table.to(DEV), torch.zeros(len(rows), dtype=torch.int32, device=DEV), _i32(rows), out, heads, kv_heads,
-                             dim, vdim, size or 0, keep, scale, cap or 0.0, slopes=slopes, sink=sink, gate=g.to(DEV)[rows].contiguous() if gate else None)
-    return out.float().cpu(), want[rows]
+                             dim, vdim, size or 0, keep, scale, cap or 0.0, slopes=slopes, sink=sink, gate=gd)
+    got = out.float().cpu()
+    if kernels.capped_mma_supports(dtype, dim, vdim) and rows == list(range(rows[0], rows[0] + len(rows))):
+        # the tensor-core kernel on the same portion (tiles of its own size, the last one short); a single row also with the
+        # four warps of a block sharing its keys; both must agree with the general kernel's answer
+        per = kernels.capped_mma_tokens_per_tile(heads, kv_heads)
+        tok0 = torch.arange(0, len(rows), per, dtype=torch.int32, device=DEV)
+        for split in ([False, True] if len(rows) == 1 else [False]):
+            tensor = torch.empty_like(out)
+            kernels.capped_attention_mma(qd, pd, table.to(DEV), _i32([0, len(rows)]), _i32([rows[-1] + 1]), torch.zeros_like(tok0), tok0, tensor,
+                                         heads, kv_heads, dim, vdim, size or 0, keep, scale, cap or 0.0, slopes=slopes, sink=sink, gate=gd,
+                                         split=split)
+            assert not torch.isnan(tensor).any(), "the tensor-core kernel read a row of a page that is gone"
+            assert _rel(tensor, want[rows]) < 3e-2, ("tensor cores", split)
+    return got, want[rows]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("sizes", [(4, 2, 16, 24, 12.0, 40, 3), (3, 3, 12, 20, None, None, 0), (6, 1, 48, 48, 8.0, 9, 20), (2, 2, 128, 64, 30.0, 33, 5),
                                    (32, 2, 16, 16, 30.0, 1, 0), (16, 2, 64, 128, 15.0, 50, 2), (3, 1, 10, 14, 25.0, 7, 1), (5, 5, 10, 200, None, 64, 64),
-                                   (1, 1, 64, 128, 1.0, 130, 17)], ids=str)
+                                   (1, 1, 64, 128, 1.0, 130, 17), (12, 3, 32, 32, 20.0, 70, 6), (40, 2, 16, 64, 10.0, 24, 40)], ids=str)
 def test_capped_window_attention_alone(dtype, sizes):
     """Grouped heads, values of another width than keys, capped scores, the distance bias, windows shorter and longer than
     a page, kept first tokens fewer and more than the window, the fixed sink and the gate, over shuffled pages."""
     heads, kv_heads, dim, vdim, cap, size, keep = sizes
-    for rows in (None, [150, 151, 199]):                    # a whole prompt; a portion whose old pages are gone
+    for rows in (None, list(range(150, 200)), [150, 151, 199], [199]):    # a whole prompt; portions and a single row whose old pages are gone
         got, want = _window_case(dtype, heads, kv_heads, dim, vdim, 200, 16, 3, cap, size, keep, rows=rows)
         assert not torch.isnan(got).any(), "a row of a page that is gone, or of another request, was read"
         assert _rel(got, want) < (1e-5 if dtype == torch.float32 else 2e-2), rows
