@@ -41,6 +41,25 @@ __global__ void gated_act_kernel(const TI* __restrict__ gu, long gu_t, T* __rest
     out[i] = from_float<T>(v * u);
 }
 
+// four entries a thread: float32 rows in 16-byte pieces, bfloat16 out in 8-byte pieces
+__global__ void gated_act_vec_kernel(const float* __restrict__ gu, long gu_t, bf16* __restrict__ out, size_t total4, int F4, int act) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total4) return;
+    const size_t row = i / F4;
+    const int c = (int)(i % F4);
+    const float4 g = reinterpret_cast<const float4*>(gu + row * gu_t)[c], u = reinterpret_cast<const float4*>(gu + row * gu_t)[F4 + c];
+    const float gs[4] = {g.x, g.y, g.z, g.w}, us[4] = {u.x, u.y, u.z, u.w};
+    float r[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float v = gs[k];
+        const float a = act == 1 ? 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v))) : v / (1.f + expf(-v));
+        r[k] = a * us[k];
+    }
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(r[0], r[1]), hi = __floats2bfloat162_rn(r[2], r[3]);
+    reinterpret_cast<uint2*>(out)[i] = make_uint2(*reinterpret_cast<const unsigned*>(&lo), *reinterpret_cast<const unsigned*>(&hi));
+}
+
 template <typename T>
 __global__ void sigmoid_gate_kernel(const T* __restrict__ x, const float* __restrict__ g, long g_t, T* __restrict__ out, size_t total, int C) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -65,6 +84,8 @@ LLMP_API int llmp_gated_act(const void* gu, int in_dtype, long gu_t, void* out, 
     const size_t total = (size_t)rows * F;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (out_dtype == LLMP_F32) gated_act_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)gu, gu_t, (float*)out, total, F, act);
+    else if (in_dtype == LLMP_F32 && F % 4 == 0 && gu_t % 4 == 0 && (size_t)gu % 16 == 0 && (size_t)out % 8 == 0)
+        gated_act_vec_kernel<<<(unsigned)((total / 4 + 255) / 256), 256, 0, stream>>>((const float*)gu, gu_t, (bf16*)out, total / 4, F / 4, act);
     else if (in_dtype == LLMP_F32) gated_act_kernel<float, bf16><<<blocks, 256, 0, stream>>>((const float*)gu, gu_t, (bf16*)out, total, F, act);
     else gated_act_kernel<bf16, bf16><<<blocks, 256, 0, stream>>>((const bf16*)gu, gu_t, (bf16*)out, total, F, act);
     return llmp_check_launch("gated_act");
