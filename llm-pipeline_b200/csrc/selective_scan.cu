@@ -11,11 +11,12 @@
 // out has the compute type. Between steps a request keeps S in its state slot, as two copies [inner][states] that take
 // turns by the parity of the last position written, so a step of one token never overwrites what it read.
 //
-// A block of 128 threads takes 128 / L channels of one request: L lanes of a warp share a channel and hold NS state entries
+// A block is one warp and takes 32 / L channels of one request (no warp waits for another; a long prompt is a chain of
+// dependent steps, and what hides their latency is the number of warps): L lanes share a channel and hold NS state entries
 // each (entry n = k L + lane, so the lanes read neighbouring words), the sum over n ends with log2(L) shuffles. The
-// request's tokens are walked in chunks of 8 with the next chunk on its way while this one is worked on: its B and C rows
-// by asynchronous copies into the other half of a shared buffer, its x, step sizes and gates as loads into registers that
-// nothing reads before the chunk's turn; one barrier a chunk. What a token needs once (its loads, the softplus, the gate,
+// request's tokens are walked in chunks of 8 with the next chunks on their way while this one is worked on: the B and C
+// rows of three chunks by asynchronous copies into a ring of stages in shared memory, x, step sizes and gates of the next
+// chunk as loads into registers that nothing reads before the chunk's turn. What a token needs once (its loads, the softplus, the gate,
 // the store) is done by one lane of the channel for it, the lanes taking a chunk's tokens in turn, so it costs a chunk one
 // pass and not eight; the walk gets a token's step size from its lane by a shuffle. The chain itself is one multiply-add
 // per token and entry. Where the output is bfloat16 they use the special-function unit's exponential and
@@ -24,8 +25,10 @@
 
 namespace {
 
-constexpr int SS_THREADS = 128;
+constexpr int SS_THREADS = 32;
 constexpr int SS_CHUNK = 8;
+constexpr int SS_AHEAD = 3;                // chunks whose inputs are under way beside the one at work
+constexpr int SS_STAGES = SS_AHEAD + 1;
 
 struct ScanArgs {
     const float* x; long x_t;
@@ -55,7 +58,7 @@ __device__ __forceinline__ void ss_cp_async_4(float* smem_dst, const float* gmem
 
 template <typename T, typename ACC, int L, int NS>
 __global__ void __launch_bounds__(SS_THREADS) selective_scan_kernel(const ScanArgs a) {
-    extern __shared__ float bc_s[];                            // [2][SS_CHUNK][2 states]
+    extern __shared__ float bc_s[];                            // the ring: SS_STAGES stages of a chunk's inputs
     constexpr int OWN = (SS_CHUNK + L - 1) / L;                // tokens of a chunk that a lane looks after
     const int r = blockIdx.x;
     const int Nst = a.states;
@@ -82,17 +85,21 @@ __global__ void __launch_bounds__(SS_THREADS) selective_scan_kernel(const ScanAr
     const float Dc = ok ? a.D[c] : 0.f;
     const bool gated = a.z != nullptr;
     T* out = reinterpret_cast<T*>(a.out);
-    const int chunk_floats = SS_CHUNK * 2 * Nst;
+    constexpr int CPW = SS_THREADS / L;                        // channels of the block
+    const int stage_floats = SS_CHUNK * 2 * Nst;               // a chunk's rows [B | C]
 
-    auto copy_bc = [&](int t0, int nt, float* dst) {           // rows [B | C] of nt tokens
+    // a chunk's B and C rows go to a stage of the ring by 4-byte asynchronous copies, SS_AHEAD chunks before their turn
+    auto copy_stage = [&](int t0, int nt, float* dst) {
         for (int tt = 0; tt < nt; ++tt) {
             for (int j = threadIdx.x; j < 2 * Nst; j += SS_THREADS)
                 ss_cp_async_4(dst + tt * 2 * Nst + j, j < Nst ? a.B + (size_t)(t0 + tt) * a.bc_t + j : a.C + (size_t)(t0 + tt) * a.bc_t + j - Nst);
         }
-        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        // rows past the portion's end take part in the chunk's arithmetic with step size 0: they must hold numbers
+        for (int j = nt * 2 * Nst + threadIdx.x; j < SS_CHUNK * 2 * Nst; j += SS_THREADS) dst[j] = 0.f;
     };
-    // a lane looks after the tokens l, l + L, .. of a chunk: it loads their x, step size and gate, takes the softplus, and
-    // at the chunk's end gates and stores their outputs; the walk gets a token's step size from its lane by a shuffle
+    // a lane looks after the tokens l, l + L, .. of a chunk: it loads their x, step size and gate (a chunk ahead, into
+    // registers that nothing reads before the chunk's turn), takes the softplus, and at the chunk's end gates and stores
+    // their outputs; the walk gets a token's step size from its lane by a shuffle
     float xr[OWN], dr[OWN], zr[OWN];
     auto load_rows = [&](int t0, int nt, float (&xv)[OWN], float (&dv)[OWN], float (&zv)[OWN]) {
 #pragma unroll
@@ -104,50 +111,70 @@ __global__ void __launch_bounds__(SS_THREADS) selective_scan_kernel(const ScanAr
             zv[o] = have && gated ? a.z[(size_t)(t0 + tt) * a.z_t + c] : 0.f;
         }
     };
-    copy_bc(begin, min(SS_CHUNK, end - begin), bc_s);
     load_rows(begin, min(SS_CHUNK, end - begin), xr, dr, zr);
-    int buf = 0;
-    for (int t0 = begin; t0 < end; t0 += SS_CHUNK, buf ^= 1) {
+    const int chunks = (end - begin + SS_CHUNK - 1) / SS_CHUNK;
+#pragma unroll
+    for (int i = 0; i < SS_AHEAD; ++i) {
+        if (i < chunks) copy_stage(begin + i * SS_CHUNK, min(SS_CHUNK, end - begin - i * SS_CHUNK), bc_s + i * stage_floats);
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    }
+    for (int i = 0; i < chunks; ++i) {
+        const int t0 = begin + i * SS_CHUNK;
         const int nt = min(SS_CHUNK, end - t0);
-        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-        __syncthreads();                                       // this chunk's rows are in; the other half was read a round ago
-        float xn[OWN], dn[OWN], zn[OWN];
-        const int t1 = t0 + SS_CHUNK;
-        const bool more = t1 < end;
-        if (more) {
-            copy_bc(t1, min(SS_CHUNK, end - t1), bc_s + (buf ^ 1) * chunk_floats);
-            load_rows(t1, min(SS_CHUNK, end - t1), xn, dn, zn);
+        asm volatile("cp.async.wait_group %0;\n" ::"n"(SS_AHEAD - 1) : "memory");
+        __syncthreads();                                       // this chunk's stage is in; the stage read a round ago is free
+        if (i + SS_AHEAD < chunks) {
+            const int t1 = t0 + SS_AHEAD * SS_CHUNK;
+            copy_stage(t1, min(SS_CHUNK, end - t1), bc_s + ((i + SS_AHEAD) % SS_STAGES) * stage_floats);
         }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+        const float* rows = bc_s + (i % SS_STAGES) * stage_floats;
+        float xn[OWN], dn[OWN], zn[OWN];
+        const bool more = i + 1 < chunks;
+        if (more) load_rows(t0 + SS_CHUNK, min(SS_CHUNK, end - t0 - SS_CHUNK), xn, dn, zn);
+        // straight-line code for the chunk, so that the tokens' independent parts (shuffles, decays, the sums over the
+        // lanes) overlap and only the multiply-adds on S form a chain. A token past the portion's end has step size 0:
+        // decay 1 and nothing added.
         ACC dts[OWN], dxs[OWN], ys[OWN];
 #pragma unroll
         for (int o = 0; o < OWN; ++o) {
-            dts[o] = ss_softplus((ACC)(dr[o] + dt_b));
+            dts[o] = o * L + l < nt ? ss_softplus((ACC)(dr[o] + dt_b)) : (ACC)0;
             dxs[o] = dts[o] * (ACC)xr[o];
             ys[o] = 0;
         }
-        const float* rows = bc_s + buf * chunk_floats;
+        ACC dtv[SS_CHUNK], dxv[SS_CHUNK], yv[SS_CHUNK];
 #pragma unroll
         for (int tt = 0; tt < SS_CHUNK; ++tt) {
-            if (tt < nt) {                                     // the same for every thread of the block
-                const int o = tt / L, owner = tt % L;
-                const ACC dtv = L > 1 ? __shfl_sync(0xffffffffu, dts[o], owner, L) : dts[o];
-                const ACC dx = L > 1 ? __shfl_sync(0xffffffffu, dxs[o], owner, L) : dxs[o];
-                const float* Bs = rows + tt * 2 * Nst;
-                const float* Cs = Bs + Nst;
-                ACC y = 0;
+            dtv[tt] = L > 1 ? __shfl_sync(0xffffffffu, dts[tt / L], tt % L, L) : dts[tt / L];
+            dxv[tt] = L > 1 ? __shfl_sync(0xffffffffu, dxs[tt / L], tt % L, L) : dxs[tt / L];
+            yv[tt] = 0;
+        }
 #pragma unroll
-                for (int k = 0; k < NS; ++k) {
-                    const int n = k * L + l;
-                    if (n < Nst) {
-                        S[k] = fma(ss_exp(dtv * (ACC)A[k]), S[k], dx * (ACC)Bs[n]);
-                        y = fma(S[k], (ACC)Cs[n], y);
-                    }
-                }
+        for (int k = 0; k < NS; ++k) {
+            const int n = k * L + l;
+            const bool have = n < Nst;
+            float Bv[SS_CHUNK], Cv[SS_CHUNK];
+            ACC dA[SS_CHUNK];
 #pragma unroll
-                for (int w = L >> 1; w > 0; w >>= 1) y += __shfl_xor_sync(0xffffffffu, y, w);
-                if (owner == l) ys[o] = y;
+            for (int tt = 0; tt < SS_CHUNK; ++tt) {
+                Bv[tt] = have ? rows[tt * 2 * Nst + n] : 0.f;
+                Cv[tt] = have ? rows[tt * 2 * Nst + Nst + n] : 0.f;
+                dA[tt] = ss_exp(dtv[tt] * (ACC)A[k]);
+            }
+#pragma unroll
+            for (int tt = 0; tt < SS_CHUNK; ++tt) {
+                S[k] = fma(dA[tt], S[k], dxv[tt] * (ACC)Bv[tt]);
+                yv[tt] = fma(S[k], (ACC)Cv[tt], yv[tt]);
             }
         }
+#pragma unroll
+        for (int w = L >> 1; w > 0; w >>= 1) {
+#pragma unroll
+            for (int tt = 0; tt < SS_CHUNK; ++tt) yv[tt] += __shfl_xor_sync(0xffffffffu, yv[tt], w);
+        }
+#pragma unroll
+        for (int tt = 0; tt < SS_CHUNK; ++tt)
+            if (tt % L == l) ys[tt / L] = yv[tt];
 #pragma unroll
         for (int o = 0; o < OWN; ++o) {
             const int tt = o * L + l;
@@ -173,9 +200,14 @@ template <int L, int NS>
 void launch_scan(const ScanArgs& a, int out_dtype, int R, cudaStream_t stream) {
     constexpr int per_block = SS_THREADS / L;
     dim3 grid(R, (unsigned)((a.inner + per_block - 1) / per_block));
-    const size_t smem = (size_t)2 * SS_CHUNK * 2 * a.states * sizeof(float);
-    if (out_dtype == LLMP_BF16) selective_scan_kernel<bf16, float, L, NS><<<grid, SS_THREADS, smem, stream>>>(a);
-    else selective_scan_kernel<float, double, L, NS><<<grid, SS_THREADS, smem, stream>>>(a);
+    const size_t smem = (size_t)SS_STAGES * SS_CHUNK * 2 * a.states * sizeof(float);
+    if (out_dtype == LLMP_BF16) {
+        LLMP_ALLOW_SMEM((selective_scan_kernel<bf16, float, L, NS>), smem);
+        selective_scan_kernel<bf16, float, L, NS><<<grid, SS_THREADS, smem, stream>>>(a);
+    } else {
+        LLMP_ALLOW_SMEM((selective_scan_kernel<float, double, L, NS>), smem);
+        selective_scan_kernel<float, double, L, NS><<<grid, SS_THREADS, smem, stream>>>(a);
+    }
 }
 
 }  // namespace
@@ -188,9 +220,11 @@ LLMP_API int llmp_selective_scan(const float* x, long x_t, const float* dt, long
     LLMP_REQUIRE(inner > 0 && states > 0 && states <= 256, "selective_scan: %d channels with %d state entries (up to 256 are served)",
                  inner, states);
     LLMP_REQUIRE(state_half >= (long)inner * states, "selective_scan: the state piece is shorter than the state");
-    // two state entries a lane up to 64 entries, then 32 lanes with more each
+    // a lane per state entry up to 32 entries, then 32 lanes with more each: a long prompt is a chain of dependent steps
+    // per warp, and what hides their latency is the number of warps (measured: 0.59 ms for 2,048 tokens of 4,096 channels
+    // with 16 entries so; 1.08 ms with 8 entries a lane, a sixth of the instructions but an eighth of the warps)
     int L = 1;
-    while (L < 32 && L * 2 < states) L *= 2;
+    while (L < 32 && L < states) L *= 2;
     const int NS = (states + L - 1) / L;
     ScanArgs a;
     a.x = x; a.x_t = x_t; a.dt = dt; a.dt_t = dt_t; a.dt_bias = dt_bias; a.B = B; a.C = C; a.bc_t = bc_t; a.A = A; a.D = D;
@@ -198,13 +232,14 @@ LLMP_API int llmp_selective_scan(const float* x, long x_t, const float* dt, long
     a.slots = slots; a.positions = positions; a.out = out; a.out_t = out_t; a.inner = inner; a.states = states; a.L = L;
     LLMP_REQUIRE(((long)inner * L + SS_THREADS - 1) / SS_THREADS <= 65535, "selective_scan: too many channels %d", inner);
     switch (L) {
-        case 1: if (NS <= 1) launch_scan<1, 1>(a, out_dtype, R, stream); else launch_scan<1, 2>(a, out_dtype, R, stream); break;
-        case 2: launch_scan<2, 2>(a, out_dtype, R, stream); break;
-        case 4: launch_scan<4, 2>(a, out_dtype, R, stream); break;
-        case 8: launch_scan<8, 2>(a, out_dtype, R, stream); break;
-        case 16: launch_scan<16, 2>(a, out_dtype, R, stream); break;
+        case 1: launch_scan<1, 1>(a, out_dtype, R, stream); break;
+        case 2: launch_scan<2, 1>(a, out_dtype, R, stream); break;
+        case 4: launch_scan<4, 1>(a, out_dtype, R, stream); break;
+        case 8: launch_scan<8, 1>(a, out_dtype, R, stream); break;
+        case 16: launch_scan<16, 1>(a, out_dtype, R, stream); break;
         default:
-            if (NS <= 2) launch_scan<32, 2>(a, out_dtype, R, stream);
+            if (NS <= 1) launch_scan<32, 1>(a, out_dtype, R, stream);
+            else if (NS <= 2) launch_scan<32, 2>(a, out_dtype, R, stream);
             else if (NS <= 4) launch_scan<32, 4>(a, out_dtype, R, stream);
             else launch_scan<32, 8>(a, out_dtype, R, stream);
     }
