@@ -68,6 +68,18 @@ __global__ void sigmoid_gate_kernel(const T* __restrict__ x, const float* __rest
     out[i] = from_float<T>(to_float(x[i]) / (1.f + expf(-gv)));
 }
 
+// four entries a thread: bfloat16 rows in 8-byte pieces, the float32 gate in 16-byte pieces
+__global__ void sigmoid_gate_vec_kernel(const bf16* __restrict__ x, const float* __restrict__ g, long g_t, bf16* __restrict__ out, size_t total4, int C4) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total4) return;
+    const float4 gv = reinterpret_cast<const float4*>(g + (i / C4) * g_t)[i % C4];
+    const uint2 raw = reinterpret_cast<const uint2*>(x)[i];
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    const __nv_bfloat162 a = __floats2bfloat162_rn(__low2float(lo) / (1.f + expf(-gv.x)), __high2float(lo) / (1.f + expf(-gv.y)));
+    const __nv_bfloat162 b = __floats2bfloat162_rn(__low2float(hi) / (1.f + expf(-gv.z)), __high2float(hi) / (1.f + expf(-gv.w)));
+    reinterpret_cast<uint2*>(out)[i] = make_uint2(*reinterpret_cast<const unsigned*>(&a), *reinterpret_cast<const unsigned*>(&b));
+}
+
 template <typename T>
 __global__ void convert_rows_kernel(const float* __restrict__ in, long in_t, T* __restrict__ out, size_t total, int C) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -95,7 +107,9 @@ LLMP_API int llmp_sigmoid_gate(const void* x, const float* g, long g_t, void* ou
     if (rows <= 0 || C <= 0) return 0;
     const size_t total = (size_t)rows * C;
     const unsigned blocks = (unsigned)((total + 255) / 256);
-    if (dtype == LLMP_BF16) sigmoid_gate_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)x, g, g_t, (bf16*)out, total, C);
+    if (dtype == LLMP_BF16 && C % 4 == 0 && g_t % 4 == 0 && (size_t)g % 16 == 0 && (size_t)x % 8 == 0 && (size_t)out % 8 == 0)
+        sigmoid_gate_vec_kernel<<<(unsigned)((total / 4 + 255) / 256), 256, 0, stream>>>((const bf16*)x, g, g_t, (bf16*)out, total / 4, C / 4);
+    else if (dtype == LLMP_BF16) sigmoid_gate_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)x, g, g_t, (bf16*)out, total, C);
     else sigmoid_gate_kernel<float><<<blocks, 256, 0, stream>>>((const float*)x, g, g_t, (float*)out, total, C);
     return llmp_check_launch("sigmoid_gate");
 }

@@ -42,10 +42,15 @@ __device__ __forceinline__ float conv_act(float v, float xin, int act) {
     return act == 1 ? v / (1.f + expf(-v)) : (act == 2 ? v + xin : v);
 }
 
-__device__ __forceinline__ void conv_store(const ConvArgs& a, int t, int c, float v) {
+// where channel c lies in the second output's first row: a thread's channel is fixed, so it divides once
+__device__ __forceinline__ size_t conv_out2_base(const ConvArgs& a, int c) {
+    return a.out2 ? (size_t)(c / a.out2_split) * a.out2_block + c % a.out2_split : 0;
+}
+
+__device__ __forceinline__ void conv_store(const ConvArgs& a, int t, int c, float v, size_t base2) {
     if (a.out) a.out[(size_t)t * a.out_t + c] = v;
     if (a.out2) {
-        const size_t at = (size_t)(c / a.out2_split) * a.out2_block + (size_t)t * a.out2_t + c % a.out2_split;
+        const size_t at = base2 + (size_t)t * a.out2_t;
         if (a.out2_bf16) reinterpret_cast<bf16*>(a.out2)[at] = __float2bfloat16_rn(v);
         else reinterpret_cast<float*>(a.out2)[at] = v;
     }
@@ -69,6 +74,7 @@ __global__ void short_conv_serial_kernel(const ConvArgs a) {
         w[j] = j < K - 1 ? rd[(size_t)j * a.C + c] : 0.f;
     }
     const float b = a.bias ? load_as_float(a.bias, a.bias_bf16, c) : 0.f;
+    const size_t base2 = conv_out2_base(a, c);
     for (int t = begin; t < end; ++t) {
         const float xin = a.x[(size_t)t * a.x_t + c];
         float acc = 0.f;
@@ -80,7 +86,7 @@ __global__ void short_conv_serial_kernel(const ConvArgs a) {
         for (int j = 0; j < CONV_MAX_TAPS; ++j)
             if (j == K - 1) last = tap[j];
         acc = fmaf(xin, last, acc);
-        conv_store(a, t, c, conv_act(acc + b, xin, a.act));
+        conv_store(a, t, c, conv_act(acc + b, xin, a.act), base2);
 #pragma unroll
         for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
             if (j < K - 1) w[j] = (j + 1 < K - 1) ? w[j + 1] : xin;
@@ -111,6 +117,7 @@ __global__ void short_conv_parallel_kernel(const ConvArgs a, const int N) {
     for (int j = 0; j < CONV_MAX_TAPS; ++j)
         if (j == K - 1) last = tap[j];
     const float b = a.bias ? load_as_float(a.bias, a.bias_bf16, c) : 0.f;
+    const size_t base2 = conv_out2_base(a, c);
     const int t1 = min(t0 + CONV_TILE_TOKENS, N);
     int r_prev = -1;
     for (int t = t0; t < t1; ++t) {
@@ -134,7 +141,7 @@ __global__ void short_conv_parallel_kernel(const ConvArgs a, const int N) {
         for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
             if (j < K - 1) acc = fmaf(w[j], tap[j], acc);
         acc = fmaf(xin, last, acc);
-        conv_store(a, t, c, conv_act(acc + b, xin, a.act));
+        conv_store(a, t, c, conv_act(acc + b, xin, a.act), base2);
 #pragma unroll
         for (int j = 0; j < CONV_MAX_TAPS - 1; ++j)
             if (j < K - 1) w[j] = (j + 1 < K - 1) ? w[j + 1] : xin;
