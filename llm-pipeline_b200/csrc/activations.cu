@@ -30,6 +30,8 @@ __global__ void scaled_sum_kernel(const float* __restrict__ a, float sa, const f
 
 template <typename TI, typename T>
 __global__ void gated_act_kernel(const TI* __restrict__ gu, long gu_t, T* __restrict__ out, size_t total, int F, int act) {
+    pdl_wait();                                    // what the kernels before wrote is complete
+    pdl_trigger();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const size_t row = i / F;
@@ -43,6 +45,8 @@ __global__ void gated_act_kernel(const TI* __restrict__ gu, long gu_t, T* __rest
 
 // four entries a thread: float32 rows in 16-byte pieces, bfloat16 out in 8-byte pieces
 __global__ void gated_act_vec_kernel(const float* __restrict__ gu, long gu_t, bf16* __restrict__ out, size_t total4, int F4, int act) {
+    pdl_wait();                                    // what the kernels before wrote is complete
+    pdl_trigger();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total4) return;
     const size_t row = i / F4;
@@ -62,6 +66,8 @@ __global__ void gated_act_vec_kernel(const float* __restrict__ gu, long gu_t, bf
 
 template <typename T>
 __global__ void sigmoid_gate_kernel(const T* __restrict__ x, const float* __restrict__ g, long g_t, T* __restrict__ out, size_t total, int C) {
+    pdl_wait();                                    // what the kernels before wrote is complete
+    pdl_trigger();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const float gv = g[(i / C) * g_t + i % C];
@@ -70,6 +76,8 @@ __global__ void sigmoid_gate_kernel(const T* __restrict__ x, const float* __rest
 
 // four entries a thread: bfloat16 rows in 8-byte pieces, the float32 gate in 16-byte pieces
 __global__ void sigmoid_gate_vec_kernel(const bf16* __restrict__ x, const float* __restrict__ g, long g_t, bf16* __restrict__ out, size_t total4, int C4) {
+    pdl_wait();                                    // what the kernels before wrote is complete
+    pdl_trigger();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total4) return;
     const float4 gv = reinterpret_cast<const float4*>(g + (i / C4) * g_t)[i % C4];
@@ -82,6 +90,8 @@ __global__ void sigmoid_gate_vec_kernel(const bf16* __restrict__ x, const float*
 
 template <typename T>
 __global__ void convert_rows_kernel(const float* __restrict__ in, long in_t, T* __restrict__ out, size_t total, int C) {
+    pdl_wait();                                    // what the kernels before wrote is complete
+    pdl_trigger();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < total) out[i] = from_float<T>(in[(i / C) * in_t + i % C]);
 }
@@ -95,11 +105,11 @@ LLMP_API int llmp_gated_act(const void* gu, int in_dtype, long gu_t, void* out, 
     LLMP_REQUIRE(in_dtype == LLMP_F32 || in_dtype == out_dtype, "gated_act: rows of the compute type give the compute type");
     const size_t total = (size_t)rows * F;
     const unsigned blocks = (unsigned)((total + 255) / 256);
-    if (out_dtype == LLMP_F32) gated_act_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)gu, gu_t, (float*)out, total, F, act);
+    if (out_dtype == LLMP_F32) llmp_launch_dependent(gated_act_kernel<float, float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, gu_t, (float*)out, total, F, act);
     else if (in_dtype == LLMP_F32 && F % 4 == 0 && gu_t % 4 == 0 && (size_t)gu % 16 == 0 && (size_t)out % 8 == 0)
-        gated_act_vec_kernel<<<(unsigned)((total / 4 + 255) / 256), 256, 0, stream>>>((const float*)gu, gu_t, (bf16*)out, total / 4, F / 4, act);
-    else if (in_dtype == LLMP_F32) gated_act_kernel<float, bf16><<<blocks, 256, 0, stream>>>((const float*)gu, gu_t, (bf16*)out, total, F, act);
-    else gated_act_kernel<bf16, bf16><<<blocks, 256, 0, stream>>>((const bf16*)gu, gu_t, (bf16*)out, total, F, act);
+        llmp_launch_dependent(gated_act_vec_kernel, dim3((unsigned)((total / 4 + 255) / 256)), dim3(256), 0, stream, (const float*)gu, gu_t, (bf16*)out, total / 4, F / 4, act);
+    else if (in_dtype == LLMP_F32) llmp_launch_dependent(gated_act_kernel<float, bf16>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, gu_t, (bf16*)out, total, F, act);
+    else llmp_launch_dependent(gated_act_kernel<bf16, bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)gu, gu_t, (bf16*)out, total, F, act);
     return llmp_check_launch("gated_act");
 }
 
@@ -108,9 +118,9 @@ LLMP_API int llmp_sigmoid_gate(const void* x, const float* g, long g_t, void* ou
     const size_t total = (size_t)rows * C;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == LLMP_BF16 && C % 4 == 0 && g_t % 4 == 0 && (size_t)g % 16 == 0 && (size_t)x % 8 == 0 && (size_t)out % 8 == 0)
-        sigmoid_gate_vec_kernel<<<(unsigned)((total / 4 + 255) / 256), 256, 0, stream>>>((const bf16*)x, g, g_t, (bf16*)out, total / 4, C / 4);
-    else if (dtype == LLMP_BF16) sigmoid_gate_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)x, g, g_t, (bf16*)out, total, C);
-    else sigmoid_gate_kernel<float><<<blocks, 256, 0, stream>>>((const float*)x, g, g_t, (float*)out, total, C);
+        llmp_launch_dependent(sigmoid_gate_vec_kernel, dim3((unsigned)((total / 4 + 255) / 256)), dim3(256), 0, stream, (const bf16*)x, g, g_t, (bf16*)out, total / 4, C / 4);
+    else if (dtype == LLMP_BF16) llmp_launch_dependent(sigmoid_gate_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)x, g, g_t, (bf16*)out, total, C);
+    else llmp_launch_dependent(sigmoid_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, g, g_t, (float*)out, total, C);
     return llmp_check_launch("sigmoid_gate");
 }
 
@@ -118,8 +128,8 @@ LLMP_API int llmp_convert_rows(const float* in, long in_t, void* out, int out_dt
     if (rows <= 0 || C <= 0) return 0;
     const size_t total = (size_t)rows * C;
     const unsigned blocks = (unsigned)((total + 255) / 256);
-    if (out_dtype == LLMP_BF16) convert_rows_kernel<bf16><<<blocks, 256, 0, stream>>>(in, in_t, (bf16*)out, total, C);
-    else convert_rows_kernel<float><<<blocks, 256, 0, stream>>>(in, in_t, (float*)out, total, C);
+    if (out_dtype == LLMP_BF16) llmp_launch_dependent(convert_rows_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, in, in_t, (bf16*)out, total, C);
+    else llmp_launch_dependent(convert_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, in, in_t, (float*)out, total, C);
     return llmp_check_launch("convert_rows");
 }
 

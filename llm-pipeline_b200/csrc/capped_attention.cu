@@ -28,6 +28,8 @@ template <typename T>
 __global__ void capped_qkv_post_kernel(const float* __restrict__ qkv, long qkv_t, const void* __restrict__ bias, int bias_bf16,
                                        float v_eps, int v_norm, T* __restrict__ q_out, long q_out_t, const int* __restrict__ slots,
                                        T* __restrict__ pages, int page_size, int H, int G, int d, int dv) {
+    pdl_wait();                                    // what the kernels before wrote is complete
+    pdl_trigger();
     const int n = blockIdx.x;
     const float* row = qkv + (size_t)n * qkv_t;
     const int slot = slots ? slots[n] : -1;
@@ -199,10 +201,10 @@ LLMP_API int llmp_capped_qkv_post(const float* qkv, long qkv_t, const void* bias
     LLMP_REQUIRE(H > 0 && G > 0 && H % G == 0 && d > 0 && dv > 0, "capped_qkv_post: bad sizes heads=%d kv=%d dim=%d vdim=%d", H, G, d, dv);
     LLMP_REQUIRE(pages == nullptr || page_size > 0, "capped_qkv_post: pages without a page size");
     if (dtype == LLMP_F32)
-        capped_qkv_post_kernel<float><<<N, 256, 0, stream>>>(qkv, qkv_t, bias, (int)(bias_dtype == LLMP_BF16), v_eps, v_norm, (float*)q_out,
+        llmp_launch_dependent(capped_qkv_post_kernel<float>, dim3(N), dim3(256), 0, stream, qkv, qkv_t, bias, (int)(bias_dtype == LLMP_BF16), v_eps, v_norm, (float*)q_out,
                                                              q_out_t, slots, (float*)pages, page_size, H, G, d, dv);
     else
-        capped_qkv_post_kernel<bf16><<<N, 256, 0, stream>>>(qkv, qkv_t, bias, (int)(bias_dtype == LLMP_BF16), v_eps, v_norm, (bf16*)q_out,
+        llmp_launch_dependent(capped_qkv_post_kernel<bf16>, dim3(N), dim3(256), 0, stream, qkv, qkv_t, bias, (int)(bias_dtype == LLMP_BF16), v_eps, v_norm, (bf16*)q_out,
                                                             q_out_t, slots, (bf16*)pages, page_size, H, G, d, dv);
     return llmp_check_launch("capped_qkv_post");
 }

@@ -11,7 +11,8 @@
 // distance, the mask; the softmax runs in units of log2 and starts from the sink (a key of that score without a value).
 // The gate, sigmoid of a float32 row, is applied as the output is stored.
 //
-// The key/value tile has two buffers: the copy of the next tile runs under the products of this one.
+// The key/value tiles go through a ring of buffers: two for prompts (the copy of the next tile runs under the products of
+// this one, and two blocks share an SM), four for steps of single tokens.
 //
 // Steps of one token a request (`split`): the tile's rows fit one warp's 16, and the four warps share the walk instead:
 // warp w takes the half tiles whose number is w modulo 4 and keeps sums of its own; at the end the four meet in shared
@@ -39,7 +40,7 @@ struct CappedMmaParams {
     long q_stride, out_stride, gate_stride;
     int table_stride;
     int nq, nkv, page_size, window, keep;
-    int heads_per_cta, tokens_per_cta, head_chunks, num_tiles, split;
+    int heads_per_cta, tokens_per_cta, head_chunks, num_tiles, split, stages;
     float scale, cap;
 };
 
@@ -90,13 +91,15 @@ constexpr float CM_LOG2E = 1.4426950408889634f;
 template <int D16, int V16>
 __global__ void __launch_bounds__(CM_THREADS, 2) capped_attention_mma_kernel(const CappedMmaParams p) {
     extern __shared__ __align__(16) unsigned char cm_smem[];
+    pdl_wait();                                    // what the kernels before wrote is complete
+    pdl_trigger();
     constexpr int D = D16 * 16, DV = V16 * 16;
     constexpr int RS = D + DV;                                   // a cached row
     constexpr int QSTRIDE = D + 8, KSTRIDE = RS + 8;             // padded rows: conflict-free ldmatrix
     bf16* Qs = reinterpret_cast<bf16*>(cm_smem);                 // [CM_ROWS][QSTRIDE]
-    bf16* ring = Qs + CM_ROWS * QSTRIDE;                         // [2][CM_KEYS][KSTRIDE]
+    bf16* ring = Qs + CM_ROWS * QSTRIDE;                         // [stages][CM_KEYS][KSTRIDE]
     constexpr int STAGE_ELEMS = CM_KEYS * KSTRIDE;
-    __shared__ long long key_off[2][CM_KEYS];
+    __shared__ long long key_off[4][CM_KEYS];
     const bool split = p.split != 0;                             // four warps on the 16 rows of a one-token tile
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -202,16 +205,30 @@ __global__ void __launch_bounds__(CM_THREADS, 2) capped_attention_mma_kernel(con
     const int warp_hi_pos = pos0 + tok0 + (warp_last_tok < ntok ? warp_last_tok : ntok - 1);
     const int warp_lo_pos = pos0 + tok0 + (warp_first_tok < ntok ? warp_first_tok : ntok - 1);
     const bf16* Qw = Qs + (size_t)(rw * 16 + (lane & 15)) * QSTRIDE + (lane >> 4) * 8;     // this lane's ldmatrix row of Q
-    if (first_tile <= hi) issue_tile(first_tile, 0);
+    // the ring: stages - 1 tiles are under way beside the one at work (every round commits one group of copies, an empty
+    // one once the walk's tiles are all asked for, so that the count of groups to wait for stays the same)
+    const int stages = p.stages;
+    int j_issue = first_tile, buf_issue = 0;
+    for (int s0 = 0; s0 < stages - 1; ++s0) {
+        if (j_issue <= hi) {
+            issue_tile(j_issue, buf_issue);
+            j_issue = next_tile(j_issue);
+        } else {
+            asm volatile("cp.async.commit_group;\n" ::: "memory");
+        }
+        buf_issue = buf_issue + 1 == stages ? 0 : buf_issue + 1;
+    }
     int buf = 0, half_no = 0;
     for (int j0 = first_tile; j0 <= hi; j0 = next_tile(j0)) {
-        const int j1 = next_tile(j0);
-        if (j1 <= hi) {
-            issue_tile(j1, buf ^ 1);                             // its buffer was read last in the round before: see the barrier below
-            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        if (j_issue <= hi) {
+            issue_tile(j_issue, buf_issue);                      // its buffer was read last in the round before: see the barrier below
+            j_issue = next_tile(j_issue);
         } else {
-            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+            asm volatile("cp.async.commit_group;\n" ::: "memory");
         }
+        buf_issue = buf_issue + 1 == stages ? 0 : buf_issue + 1;
+        if (stages == 4) asm volatile("cp.async.wait_group 3;\n" ::: "memory");
+        else asm volatile("cp.async.wait_group 1;\n" ::: "memory");
         __syncthreads();
         const bf16* KVs = ring + (size_t)buf * STAGE_ELEMS;
         if (warp_has_rows) {
@@ -304,7 +321,7 @@ __global__ void __launch_bounds__(CM_THREADS, 2) capped_attention_mma_kernel(con
             half_no += 2;
         }
         __syncthreads();                                         // the tile's buffer may be overwritten now
-        buf ^= 1;
+        buf = buf + 1 == stages ? 0 : buf + 1;
     }
     asm volatile("cp.async.wait_group 0;\n" ::: "memory");       // the query copy, where no key tile followed it
 
@@ -379,11 +396,16 @@ template <int D16, int V16>
 int launch_capped_mma(const CappedMmaParams& p, unsigned grid, cudaStream_t stream) {
     const size_t q_bytes = sizeof(bf16) * (size_t)CM_ROWS * (D16 * 16 + 8);
     const size_t stage = sizeof(bf16) * (size_t)CM_KEYS * (D16 * 16 + V16 * 16 + 8);
-    size_t smem = q_bytes + 2 * stage;
+    // two buffers for prompts, so that two blocks share an SM; four for steps of single tokens, whose few blocks are each a
+    // chain of copies that should be under way early
+    CappedMmaParams q = p;
+    q.stages = (p.split && q_bytes + 4 * stage <= 200 * 1024) ? 4 : 2;
+    size_t smem = q_bytes + q.stages * stage;
     const size_t meet = sizeof(float) * 3 * 32 * (size_t)(8 * V16 + 4);          // where the warps of a one-token tile meet
     if (smem < meet) smem = meet;
-    LLMP_ALLOW_SMEM((capped_attention_mma_kernel<D16, V16>), smem);
-    capped_attention_mma_kernel<D16, V16><<<grid, CM_THREADS, smem, stream>>>(p);
+    // the kernel also has 2 KB of static shared memory: ask for the larger limit as soon as the two together pass 48 KB
+    LLMP_ALLOW_SMEM((capped_attention_mma_kernel<D16, V16>), smem + 4096);
+    llmp_launch_dependent(capped_attention_mma_kernel<D16, V16>, dim3(grid), dim3(CM_THREADS), smem, stream, q);
     return 0;
 }
 
@@ -418,6 +440,7 @@ LLMP_API int llmp_capped_attention_mma(const void* q, long q_stride, void* out, 
     p.head_chunks = (G + p.heads_per_cta - 1) / p.heads_per_cta;
     p.num_tiles = num_tiles;
     p.split = split ? 1 : 0;
+    p.stages = 2;
     LLMP_REQUIRE((long)num_tiles * nkv * p.head_chunks < (1L << 31), "capped_attention_mma: too many tiles");
     LLMP_REQUIRE((q_stride % 8) == 0 && (out_stride % 2) == 0 && ((size_t)q % 16) == 0 && ((size_t)pages % 16) == 0 &&
                  ((size_t)out % 4) == 0 && (gate == nullptr || ((gate_stride % 2) == 0 && ((size_t)gate % 8) == 0)),

@@ -80,6 +80,8 @@ __global__ void latent_rows_post_kernel(const float* __restrict__ q, long q_t, c
                                         const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot_dims, int interleaved,
                                         T* __restrict__ q_out, long q_out_t, const int* __restrict__ slots, T* __restrict__ pages) {
     __shared__ float scratch[32];
+    pdl_wait();                                    // what the kernels before wrote is complete
+    pdl_trigger();
     const int n = blockIdx.x;
     const int half = rot_dims / 2;
     const float* cs = cos_t + (size_t)n * half;
@@ -133,10 +135,10 @@ LLMP_API int llmp_latent_rows_post(const float* q, long q_t, const float* dkv, l
     LLMP_REQUIRE(rot_dims == 0 || (cos_t && sin_t), "latent_rows_post: a rotation needs its tables");
     LLMP_REQUIRE(dkv == nullptr || pages == nullptr || norm_w != nullptr, "latent_rows_post: the latent's norm weight is missing");
     if (dtype == LLMP_F32)
-        latent_rows_post_kernel<float><<<N, 128, 0, stream>>>(q, q_t, dkv, dkv_t, H, d, r, rank, norm_w, (int)(norm_w_dtype == LLMP_BF16), eps,
+        llmp_launch_dependent(latent_rows_post_kernel<float>, dim3(N), dim3(128), 0, stream, q, q_t, dkv, dkv_t, H, d, r, rank, norm_w, (int)(norm_w_dtype == LLMP_BF16), eps,
                                                               cos_t, sin_t, rot_dims, interleaved, (float*)q_out, q_out_t, slots, (float*)pages);
     else
-        latent_rows_post_kernel<bf16><<<N, 128, 0, stream>>>(q, q_t, dkv, dkv_t, H, d, r, rank, norm_w, (int)(norm_w_dtype == LLMP_BF16), eps,
+        llmp_launch_dependent(latent_rows_post_kernel<bf16>, dim3(N), dim3(128), 0, stream, q, q_t, dkv, dkv_t, H, d, r, rank, norm_w, (int)(norm_w_dtype == LLMP_BF16), eps,
                                                              cos_t, sin_t, rot_dims, interleaved, (bf16*)q_out, q_out_t, slots, (bf16*)pages);
     return llmp_check_launch("latent_rows_post");
 }

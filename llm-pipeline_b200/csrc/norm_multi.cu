@@ -38,6 +38,8 @@ __device__ __forceinline__ float nm_value(const NormMultiArgs& p, size_t row, in
 
 __global__ void __launch_bounds__(NM_THREADS) add_rmsnorm_multi_kernel(const NormMultiArgs p) {
     __shared__ float scratch[32];
+    pdl_wait();                                    // what the kernels before wrote is complete
+    pdl_trigger();
     const int m = blockIdx.x;
     const size_t row = p.rows ? (size_t)p.rows[m] : (size_t)m;
     const int D = p.D;
@@ -102,6 +104,8 @@ __device__ __forceinline__ float4 nm_load4(const void* p, int is_bf16, size_t i4
 
 __global__ void __launch_bounds__(NM_THREADS) add_rmsnorm_multi_vec_kernel(const NormMultiArgs p) {
     __shared__ float scratch[32];
+    pdl_wait();                                    // what the kernels before wrote is complete
+    pdl_trigger();
     const int m = blockIdx.x;
     const size_t row = p.rows ? (size_t)p.rows[m] : (size_t)m;
     const int D4 = p.D >> 2;
@@ -159,7 +163,7 @@ LLMP_API int llmp_add_rmsnorm_multi(float* residual, const void* a, int a_dtype,
     auto aligned = [](const void* q, int bf) { return q == nullptr || ((size_t)q % (bf ? 8 : 16)) == 0; };
     const bool vec = D % 4 == 0 && D <= 4 * NM_THREADS * NM_PIECES && out_block % 4 == 0 && out_row % 4 == 0 && aligned(residual, 0) &&
                      aligned(a, p.a_bf16) && aligned(b, p.b_bf16) && aligned(bias, p.bias_bf16) && aligned(w, p.w_bf16) && aligned(out, p.out_bf16);
-    if (vec) add_rmsnorm_multi_vec_kernel<<<M, NM_THREADS, 0, stream>>>(p);
-    else add_rmsnorm_multi_kernel<<<M, NM_THREADS, 0, stream>>>(p);
+    if (vec) llmp_launch_dependent(add_rmsnorm_multi_vec_kernel, dim3(M), dim3(NM_THREADS), 0, stream, p);
+    else llmp_launch_dependent(add_rmsnorm_multi_kernel, dim3(M), dim3(NM_THREADS), 0, stream, p);
     return llmp_check_launch("add_rmsnorm_multi");
 }

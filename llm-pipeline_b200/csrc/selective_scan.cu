@@ -59,6 +59,8 @@ __device__ __forceinline__ void ss_cp_async_4(float* smem_dst, const float* gmem
 template <typename T, typename ACC, int L, int NS>
 __global__ void __launch_bounds__(SS_THREADS) selective_scan_kernel(const ScanArgs a) {
     extern __shared__ float bc_s[];                            // the ring: SS_STAGES stages of a chunk's inputs
+    pdl_wait();                                    // what the kernels before wrote is complete
+    pdl_trigger();
     constexpr int OWN = (SS_CHUNK + L - 1) / L;                // tokens of a chunk that a lane looks after
     const int r = blockIdx.x;
     const int Nst = a.states;
@@ -203,10 +205,10 @@ void launch_scan(const ScanArgs& a, int out_dtype, int R, cudaStream_t stream) {
     const size_t smem = (size_t)SS_STAGES * SS_CHUNK * 2 * a.states * sizeof(float);
     if (out_dtype == LLMP_BF16) {
         LLMP_ALLOW_SMEM((selective_scan_kernel<bf16, float, L, NS>), smem);
-        selective_scan_kernel<bf16, float, L, NS><<<grid, SS_THREADS, smem, stream>>>(a);
+        llmp_launch_dependent(selective_scan_kernel<bf16, float, L, NS>, grid, dim3(SS_THREADS), smem, stream, a);
     } else {
         LLMP_ALLOW_SMEM((selective_scan_kernel<float, double, L, NS>), smem);
-        selective_scan_kernel<float, double, L, NS><<<grid, SS_THREADS, smem, stream>>>(a);
+        llmp_launch_dependent(selective_scan_kernel<float, double, L, NS>, grid, dim3(SS_THREADS), smem, stream, a);
     }
 }
 

@@ -57,6 +57,8 @@ __device__ __forceinline__ void conv_store(const ConvArgs& a, int t, int c, floa
 }
 
 __global__ void short_conv_serial_kernel(const ConvArgs a) {
+    pdl_wait();                                    // what the kernels before wrote is complete
+    pdl_trigger();
     const int r = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= a.C) return;
@@ -198,7 +200,7 @@ LLMP_API int llmp_short_conv(const float* x, long x_t, const void* taps, int tap
     const int col_blocks = (C + threads - 1) / threads;
     LLMP_REQUIRE(col_blocks <= 65535, "short_conv: too many channels %d", C);
     if (max_q_len <= CONV_SERIAL_TOKENS) {
-        short_conv_serial_kernel<<<dim3(R, col_blocks), threads, 0, stream>>>(a);
+        llmp_launch_dependent(short_conv_serial_kernel, dim3(R, col_blocks), dim3(threads), 0, stream, a);
         return llmp_check_launch("short_conv");
     }
     short_conv_parallel_kernel<<<dim3((N + CONV_TILE_TOKENS - 1) / CONV_TILE_TOKENS, col_blocks), threads, 0, stream>>>(a, N);
