@@ -14,10 +14,13 @@
 // The key/value tiles go through a ring of buffers: two for prompts (the copy of the next tile runs under the products of
 // this one, and two blocks share an SM), four for steps of single tokens.
 //
-// Steps of one token a request (`split`): the tile's rows fit one warp's 16, and the four warps share the walk instead:
-// warp w takes the half tiles whose number is w modulo 4 and keeps sums of its own; at the end the four meet in shared
-// memory and warp 0 adds them in their order and stores.
+// Steps of one token a request (`split`): the tile's rows fit one warp's 16, and the four warps share every tile instead:
+// warp w takes keys 16 w to 16 w + 15 of it and keeps sums of its own; at the end the four meet in shared memory and warp 0
+// adds them in their order and stores. (With whole half tiles dealt out in turn, two warps worked while two waited at the
+// tile's barrier: 2.0 against 1.5 microseconds a tile at keys and values of 128.)
 #include "common.cuh"
+
+#include <type_traits>
 
 #define CM_ROWS 64
 #define CM_KEYS 64
@@ -153,17 +156,21 @@ __global__ void __launch_bounds__(CM_THREADS, 2) capped_attention_mma_kernel(con
     asm volatile("cp.async.commit_group;\n" ::: "memory");
 
     constexpr int KVEC = RS / 8;
-    auto issue_tile = [&](int j0, int buf) {
+    // A tile's copy has two parts: where its 64 rows lie (a look into the block table by the first 64 threads, whose
+    // answer travels while the tile before is worked on and is written to shared memory before that round's last
+    // barrier), and the copy itself, which reads those places a round later.
+    auto plan_tile = [&](int j0) -> long long {
+        long long off = -1;
         if (tid < CM_KEYS) {
             const int j = j0 + tid;
-            long long off = -1;
             if (j <= hi && (j >= lo || j < keep_end)) {
                 const int page = table[j / p.page_size];
                 if (page >= 0) off = (long long)(((size_t)page * p.nkv + kvh) * p.page_size + (j % p.page_size)) * RS;
             }
-            key_off[buf][tid] = off;
         }
-        __syncthreads();
+        return off;
+    };
+    auto copy_tile = [&](int buf) {
         bf16* dst = ring + (size_t)buf * STAGE_ELEMS;
         for (int e = tid; e < CM_KEYS * KVEC; e += CM_THREADS) {
             const int key = e / KVEC, c = (e % KVEC) * 8;
@@ -208,118 +215,131 @@ __global__ void __launch_bounds__(CM_THREADS, 2) capped_attention_mma_kernel(con
     // the ring: stages - 1 tiles are under way beside the one at work (every round commits one group of copies, an empty
     // one once the walk's tiles are all asked for, so that the count of groups to wait for stays the same)
     const int stages = p.stages;
+    int j_plan = first_tile;                                     // the next tile to look up
+    for (int s0 = 0; s0 < stages; ++s0) {                        // the first tiles' places: all lookups in flight together
+        if (tid < CM_KEYS) key_off[s0][tid] = j_plan <= hi ? plan_tile(j_plan) : -1;
+        if (j_plan <= hi) j_plan = next_tile(j_plan);
+    }
+    __syncthreads();
     int j_issue = first_tile, buf_issue = 0;
     for (int s0 = 0; s0 < stages - 1; ++s0) {
         if (j_issue <= hi) {
-            issue_tile(j_issue, buf_issue);
+            copy_tile(buf_issue);
             j_issue = next_tile(j_issue);
         } else {
             asm volatile("cp.async.commit_group;\n" ::: "memory");
         }
         buf_issue = buf_issue + 1 == stages ? 0 : buf_issue + 1;
     }
-    int buf = 0, half_no = 0;
+    int buf = 0;
     for (int j0 = first_tile; j0 <= hi; j0 = next_tile(j0)) {
         if (j_issue <= hi) {
-            issue_tile(j_issue, buf_issue);                      // its buffer was read last in the round before: see the barrier below
+            copy_tile(buf_issue);                                // its buffer was read last in the round before: see the barrier below
             j_issue = next_tile(j_issue);
         } else {
             asm volatile("cp.async.commit_group;\n" ::: "memory");
         }
+        // the places of the tile that this round's buffer takes next: asked for now, written down at the round's end
+        const bool planning = j_plan <= hi;
+        const long long off_next = planning ? plan_tile(j_plan) : -1;
+        if (planning) j_plan = next_tile(j_plan);
         buf_issue = buf_issue + 1 == stages ? 0 : buf_issue + 1;
         if (stages == 4) asm volatile("cp.async.wait_group 3;\n" ::: "memory");
         else asm volatile("cp.async.wait_group 1;\n" ::: "memory");
         __syncthreads();
         const bf16* KVs = ring + (size_t)buf * STAGE_ELEMS;
-        if (warp_has_rows) {
+        // the part of a tile that starts at its key `kbase` and has NB blocks of 8 keys: scores, softmax step, values
+        auto part = [&](auto nbc, const int kbase) {
+            constexpr int NB = decltype(nbc)::value;
+            const int jh = j0 + kbase;
+            if (jh > warp_hi_pos) return;                        // every row of this warp lies before these keys
+            const bool kept = jh < p.keep;                       // kept first tokens stay in sight of every row
+            if (!kept && p.window > 0 && jh + NB * 8 - 1 < warp_lo_pos - p.window + 1) return;    // or sees none of them any more
+            float s[NB][4];
 #pragma unroll
-            for (int half = 0; half < 2; ++half, ++half_no) {
-                const int jh = j0 + half * 32;
-                if (split && (half_no & 3) != warp) continue;    // another warp's keys
-                if (jh > warp_hi_pos) continue;                  // every row of this warp lies before these keys
-                const bool kept = jh < p.keep;                   // kept first tokens stay in sight of every row
-                if (!kept && p.window > 0 && jh + 31 < warp_lo_pos - p.window + 1) continue;    // or sees none of them any more
-                float s[4][4];
+            for (int nb = 0; nb < NB; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
 #pragma unroll
-                for (int nb = 0; nb < 4; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
+            for (int ks = 0; ks < D16; ++ks) {
+                unsigned qa[4];
+                cm_ldmatrix_x4(qa, Qw + ks * 16);
 #pragma unroll
-                for (int ks = 0; ks < D16; ++ks) {
-                    unsigned qa[4];
-                    cm_ldmatrix_x4(qa, Qw + ks * 16);
-#pragma unroll
-                    for (int nb = 0; nb < 4; nb += 2) {
-                        unsigned kf[4];
-                        cm_ldmatrix_x4(kf, KVs + (size_t)(half * 32 + (nb + (lane >> 4)) * 8 + (lane & 7)) * KSTRIDE + ks * 16 +
-                                               ((lane >> 3) & 1) * 8);
-                        cm_mma(s[nb], qa, kf[0], kf[1]);
-                        cm_mma(s[nb + 1], qa, kf[2], kf[3]);
-                    }
-                }
-                // scores in units of log2: scale (and cap), the distance bias, the mask
-                float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-                for (int nb = 0; nb < 4; ++nb) {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const int j = jh + nb * 8 + 2 * t + (c & 1);
-                        const int pos = row_pos[c >> 1];
-                        float v = p.cap > 0.f ? cap_log2 * cm_tanh(s[nb][c] * inv_cap) : s[nb][c] * scale_log2;
-                        v = fmaf(-slope2[c >> 1], (float)(pos - j), v);
-                        const bool ok = j <= pos && (p.window <= 0 || j >= pos - p.window + 1 || j < p.keep);
-                        v = ok ? v : -INFINITY;
-                        s[nb][c] = v;
-                        mx[c >> 1] = fmaxf(mx[c >> 1], v);
-                    }
-                }
-                float alpha[2], m_use[2];
-#pragma unroll
-                for (int h2 = 0; h2 < 2; ++h2) {
-                    mx[h2] = fmaxf(mx[h2], __shfl_xor_sync(0xffffffffu, mx[h2], 1));
-                    mx[h2] = fmaxf(mx[h2], __shfl_xor_sync(0xffffffffu, mx[h2], 2));
-                    const float m_new = fmaxf(m_run[h2], mx[h2]);
-                    alpha[h2] = (m_new > -INFINITY) ? cm_ex2(m_run[h2] - m_new) : 1.f;
-                    m_run[h2] = m_new;
-                    m_use[h2] = (m_new > -INFINITY) ? m_new : 0.f;          // a row without any key keeps p = 2^(-inf) = 0
-                }
-                float sum[2] = {0.f, 0.f};
-#pragma unroll
-                for (int nb = 0; nb < 4; ++nb) {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const float pr = cm_ex2(s[nb][c] - m_use[c >> 1]);
-                        s[nb][c] = pr;
-                        sum[c >> 1] += pr;
-                    }
-                }
-                l_run[0] = l_run[0] * alpha[0] + sum[0];
-                l_run[1] = l_run[1] * alpha[1] + sum[1];
-                if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
-#pragma unroll
-                    for (int i = 0; i < 2 * V16; ++i) {
-                        o[i][0] *= alpha[0]; o[i][1] *= alpha[0]; o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
-                    }
-                }
-                // O += P V, 16 keys per step
-#pragma unroll
-                for (int kk = 0; kk < 2; ++kk) {
-                    unsigned pa[4];
-                    pa[0] = cm_pack(s[2 * kk][0], s[2 * kk][1]);
-                    pa[1] = cm_pack(s[2 * kk][2], s[2 * kk][3]);
-                    pa[2] = cm_pack(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-                    pa[3] = cm_pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
-#pragma unroll
-                    for (int nb2 = 0; nb2 < V16; ++nb2) {
-                        unsigned v[4];
-                        cm_ldmatrix_x4_trans(v, KVs + (size_t)(half * 32 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KSTRIDE + D +
-                                                    nb2 * 16 + (lane >> 4) * 8);
-                        cm_mma(o[nb2 * 2], pa, v[0], v[1]);
-                        cm_mma(o[nb2 * 2 + 1], pa, v[2], v[3]);
-                    }
+                for (int nb = 0; nb < NB; nb += 2) {
+                    unsigned kf[4];
+                    cm_ldmatrix_x4(kf, KVs + (size_t)(kbase + (nb + (lane >> 4)) * 8 + (lane & 7)) * KSTRIDE + ks * 16 +
+                                           ((lane >> 3) & 1) * 8);
+                    cm_mma(s[nb], qa, kf[0], kf[1]);
+                    cm_mma(s[nb + 1], qa, kf[2], kf[3]);
                 }
             }
-        } else {
-            half_no += 2;
+            // scores in units of log2: scale (and cap), the distance bias, the mask
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int j = jh + nb * 8 + 2 * t + (c & 1);
+                    const int pos = row_pos[c >> 1];
+                    float v = p.cap > 0.f ? cap_log2 * cm_tanh(s[nb][c] * inv_cap) : s[nb][c] * scale_log2;
+                    v = fmaf(-slope2[c >> 1], (float)(pos - j), v);
+                    const bool ok = j <= pos && (p.window <= 0 || j >= pos - p.window + 1 || j < p.keep);
+                    v = ok ? v : -INFINITY;
+                    s[nb][c] = v;
+                    mx[c >> 1] = fmaxf(mx[c >> 1], v);
+                }
+            }
+            float alpha[2], m_use[2];
+#pragma unroll
+            for (int h2 = 0; h2 < 2; ++h2) {
+                mx[h2] = fmaxf(mx[h2], __shfl_xor_sync(0xffffffffu, mx[h2], 1));
+                mx[h2] = fmaxf(mx[h2], __shfl_xor_sync(0xffffffffu, mx[h2], 2));
+                const float m_new = fmaxf(m_run[h2], mx[h2]);
+                alpha[h2] = (m_new > -INFINITY) ? cm_ex2(m_run[h2] - m_new) : 1.f;
+                m_run[h2] = m_new;
+                m_use[h2] = (m_new > -INFINITY) ? m_new : 0.f;          // a row without any key keeps p = 2^(-inf) = 0
+            }
+            float sum[2] = {0.f, 0.f};
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float pr = cm_ex2(s[nb][c] - m_use[c >> 1]);
+                    s[nb][c] = pr;
+                    sum[c >> 1] += pr;
+                }
+            }
+            l_run[0] = l_run[0] * alpha[0] + sum[0];
+            l_run[1] = l_run[1] * alpha[1] + sum[1];
+            if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+                for (int i = 0; i < 2 * V16; ++i) {
+                    o[i][0] *= alpha[0]; o[i][1] *= alpha[0]; o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+                }
+            }
+            // O += P V, 16 keys per step
+#pragma unroll
+            for (int kk = 0; kk < NB / 2; ++kk) {
+                unsigned pa[4];
+                pa[0] = cm_pack(s[2 * kk][0], s[2 * kk][1]);
+                pa[1] = cm_pack(s[2 * kk][2], s[2 * kk][3]);
+                pa[2] = cm_pack(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                pa[3] = cm_pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                for (int nb2 = 0; nb2 < V16; ++nb2) {
+                    unsigned v[4];
+                    cm_ldmatrix_x4_trans(v, KVs + (size_t)(kbase + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KSTRIDE + D +
+                                                nb2 * 16 + (lane >> 4) * 8);
+                    cm_mma(o[nb2 * 2], pa, v[0], v[1]);
+                    cm_mma(o[nb2 * 2 + 1], pa, v[2], v[3]);
+                }
+            }
+        };
+        if (split) {
+            part(std::integral_constant<int, 2>{}, warp * 16);  // a quarter of the tile's keys for each of the four warps
+        } else if (warp_has_rows) {
+            part(std::integral_constant<int, 4>{}, 0);
+            part(std::integral_constant<int, 4>{}, 32);
         }
+        if (tid < CM_KEYS) key_off[buf][tid] = off_next;         // this round's tile was copied long ago: its places make room
         __syncthreads();                                         // the tile's buffer may be overwritten now
         buf = buf + 1 == stages ? 0 : buf + 1;
     }

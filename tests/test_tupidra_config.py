@@ -167,3 +167,19 @@ def test_the_plain_implementation_is_causal_and_its_mechanisms_have_their_closed
     head, S = plain.scan(x[:4], dt[:4], A, B[:4], C[:4], torch.ones(3, dtype=torch.float64))
     tail, _ = plain.scan(x[4:], dt[4:], A, B[4:], C[4:], torch.ones(3, dtype=torch.float64), S)
     assert torch.allclose(torch.cat([head, tail]), whole_y)
+
+
+def test_a_random_model_folder_can_be_written_and_read_back(tmp_path):
+    from llm_pipeline_b200.config import load_config
+    from llm_pipeline_b200.models import build_model
+    from llm_pipeline_b200.weights import write_random_model
+    from llm_pipeline_b200.weights.source import SafetensorsSource, check_names_and_shapes
+
+    folder = write_random_model(T.CONFIGS["mixed"], 3, str(tmp_path))
+    config = load_config(folder)
+    assert config.architecture == "Tupidra"
+    source = SafetensorsSource(folder)
+    check_names_and_shapes(build_model(config).expected_params(), source)
+    assert abs(float(source.get("l0.norm1").float().mean()) - 1.0) < 0.3          # around one, not noise around zero
+    assert source.shape("l5.mix.uq") == (2 * (24 + 8), 12) and "l5.mix.dkv" not in source.names()
+    source.close()
