@@ -868,10 +868,10 @@ def nufolix_work(z, tokens, keys_per_token, decode, requests=1):
 # Qwen3 dense decoder of the same width, depth and vocabulary.
 TUPIDRA_SIZES = {
     "1k": {"width": 1024, "inner": 2048, "state": 16, "dt_rank": 64, "conv": 4, "taps": 4, "heads": 8, "kv_heads": 4, "dim": 128,
-           "vdim": 128, "window": 1024, "keep": 4, "lat_heads": 8, "lat_dim": 64, "rot": 32, "lat_vdim": 64, "rank": 256, "q_rank": 384,
+           "vdim": 128, "window": 1024, "keep": 8, "lat_heads": 8, "lat_dim": 64, "rot": 32, "lat_vdim": 64, "rank": 256, "q_rank": 384,
            "ff": 4096, "layers": 4, "vocab": 32000, "qwen_heads": (8, 4)},
     "2k": {"width": 2048, "inner": 4096, "state": 16, "dt_rank": 128, "conv": 4, "taps": 4, "heads": 16, "kv_heads": 4, "dim": 128,
-           "vdim": 128, "window": 1024, "keep": 4, "lat_heads": 16, "lat_dim": 128, "rot": 64, "lat_vdim": 128, "rank": 512, "q_rank": 768,
+           "vdim": 128, "window": 1024, "keep": 8, "lat_heads": 16, "lat_dim": 128, "rot": 64, "lat_vdim": 128, "rank": 512, "q_rank": 768,
            "ff": 8192, "layers": 4, "vocab": 32000, "qwen_heads": (16, 8)},
 }
 
@@ -880,7 +880,7 @@ def tupidra_config(z):
     mlp = {"kind": "dense", "ff": z["ff"]}
     latent = {"heads": z["lat_heads"], "dim": z["lat_dim"], "rot_dim": z["rot"], "vdim": z["lat_vdim"], "kv_rank": z["rank"],
               "q_rank": z["q_rank"], "scale": (z["lat_dim"] + z["rot"]) ** -0.5,
-              "rot": {"base": 500000.0, "dims": z["rot"], "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+              "rot": {"base": 10000.0, "dims": z["rot"], "scaling": {"factor": 8.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}
     kinds = [{"type": "mamba1", "mixer": {"inner": z["inner"], "state": z["state"], "dt_rank": z["dt_rank"], "conv": z["conv"]}, "mlp": mlp},
              {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"],
                                              "scale": z["dim"] ** -0.5, "softcap": 30.0, "mask": {"size": z["window"], "keep_first": z["keep"]}},
@@ -888,7 +888,7 @@ def tupidra_config(z):
              {"type": "latent_attention", "mixer": latent, "mlp": mlp},
              {"type": "latent_attention", "mixer": {**latent, "kv_from": 2}, "mlp": mlp}]
     layers = [kinds[i % 4] if i % 4 != 3 else {**kinds[3], "mixer": {**latent, "kv_from": i - 1}} for i in range(z["layers"])]
-    return {"architecture": "Tupidra", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "canon": {"taps": z["taps"]},
+    return {"architecture": "Tupidra", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "canon": {"taps": z["taps"]},
             "layers": layers}
 
 
